@@ -501,22 +501,23 @@ B200_API int b200_heads_to_rows(void* out, const void* in, const void* gate /*nu
                                 int64_t H, int64_t d, int dtype, b200_stream_t stream);
 /* Latent attention, per token: cache[slot] = [rmsnorm(dkv[:rank]) * c_norm_weight | rope(dkv[rank:rank+rd])]
  * and rope in place on columns [dim, dim + rd) of each of q's H heads of width dim + rd.  The first `dims`
- * entries of a rotary part rotate as interleaved pairs (2i, 2i+1) by positions * inv_freq[i]; cos and sin are
- * multiplied by `mult`. */
+ * entries of a rotary part rotate as interleaved pairs (2i, 2i+1), or with half_pairs as pairs (i, i + dims/2),
+ * by positions * inv_freq[i]; cos and sin are multiplied by `mult`. */
 B200_API int b200_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t ld_dkv, void* cache, int64_t ldc,
                                  const float* c_norm_weight, const float* inv_freq, float mult,
                                  const int32_t* positions, const int32_t* slots, int64_t rows, int64_t H,
-                                 int64_t dim, int64_t rd, int64_t dims, int64_t rank, float eps, int dtype,
-                                 b200_stream_t stream);
+                                 int64_t dim, int64_t rd, int64_t dims, int64_t rank, float eps, int half_pairs,
+                                 int dtype, b200_stream_t stream);
 /* out[h, t, :rank] = sum_j softmax_j((q_absorbed[h, t] . c_j + q_rot[t, h] . kr_j) * scale) c_j over the
- * cached rows j <= position of t (paged).  q_absorbed: fp32 or T, [H, rows, rank] by strides. */
+ * cached rows j <= position of t (paged), with window > 0 only over the rows with position - j < window.
+ * q_absorbed: fp32 or T, [H, rows, rank] by strides. */
 B200_API int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_stride, const void* q_absorbed,
                               int64_t qa_head_stride, int64_t qa_token_stride, int qa_is_fp32, const void* q,
                               int64_t ldq, const void* cache, int64_t ldc, const int32_t* q_cu_lens,
                               const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
                               const int32_t* token_seq, int64_t rows, int64_t H, int64_t dim, int64_t rd,
-                              int64_t rank, int64_t block_size, float scale, int n_splits, void* workspace,
-                              int64_t workspace_bytes, int dtype, b200_stream_t stream);
+                              int64_t rank, int64_t block_size, float scale, int64_t window, int n_splits,
+                              void* workspace, int64_t workspace_bytes, int dtype, b200_stream_t stream);
 /* n_splits >= 1 (bf16 only): tensor-core form, the keys of every row cut into n_splits ranges that run as
  * separate CTAs and are merged by a second kernel (n_splits > 1 needs the workspace below); n_splits = 0: the
  * CUDA-core form (any dtype, fp32 arithmetic throughout). */
@@ -550,8 +551,14 @@ B200_API int b200_grouped_gemv(void* C, int64_t ldc, const void* A, int64_t lda,
 B200_API int b200_moe_gather(void* xs, const void* h, int64_t ldh, const int32_t* sorted_pair,
                              const float* pair_scale /*nullable*/, int64_t top, int64_t n_pairs, int64_t W, int dtype,
                              b200_stream_t stream);
+/* out[row] = scale * sum_k Y[pos_of_pair[row, k]] (+ addend[row], a result that every token gets). */
 B200_API int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
-                              int64_t W, int64_t top, int dtype, b200_stream_t stream);
+                              int64_t W, int64_t top, float scale, const void* addend /*nullable*/, int64_t ld_add,
+                              int dtype, b200_stream_t stream);
+/* Experts chosen by the token id, not by a router: expert_ids[row, k] = table[tokens[row], k] (table int32
+ * [vocab, top]). */
+B200_API int b200_moe_table_route(int32_t* expert_ids, const int32_t* table, const int32_t* tokens, int64_t rows,
+                                  int64_t top, int64_t vocab, int64_t E, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------
  * Decoders with a normalised sublayer RESULT, a depth-weighted average of layer results, a minimal gated
@@ -659,6 +666,55 @@ B200_API int b200_diff_attn_decode_tc(void* out, int64_t ldo, const float* q, co
                                       int64_t window, int64_t keep_first, float lambda, float out_scale, float eps,
                                       int64_t n_splits, float* workspace /*nullable*/, int64_t workspace_floats,
                                       int dtype, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------
+ * Decoders that normalise AFTER the residual sum with one gain per row, attend with unit-length queries and keys
+ * under a distance bias and a learned sink, and cap their logits (postnorm.cu, sink_attn.cu).  The reference has
+ * no such operators; each entry states its arithmetic.  Conventions as in the blocks above.
+ * ------------------------------------------------------------------------ */
+/* s = alpha x_in + y ; x_out = s / sqrt(mean(s^2) + eps) * weight[i * weight_stride] (stride 0: one number for the
+ * row) ; h_out (nullable) = x_out as T.  x fp32 [rows, W]; y T with row stride ldy. */
+B200_API int b200_sumnorm_residual(float* x_out, void* h_out /*nullable*/, const float* x_in, const void* y,
+                                   int64_t ldy, const float* weight, int64_t weight_stride, int64_t rows, int64_t W,
+                                   float alpha, float eps, int dtype, b200_stream_t stream);
+/* The same fed by the split-K partials [n_slots][rows][W] of the matrix product that makes y (plan6:
+ * b200_dense_splitk_plan); their sum is rounded to T first. */
+B200_API int b200_sumnorm_residual_splitk(float* x_out, void* h_out /*nullable*/, const float* x_in,
+                                          const float* partials, int64_t n_slots, const int32_t* plan6,
+                                          const float* weight, int64_t weight_stride, int64_t rows, int64_t W,
+                                          float alpha, float eps, int dtype, b200_stream_t stream);
+/* out = cap * tanh(in / cap), elementwise (may be in place). */
+B200_API int b200_softcap(void* out, const void* in, int64_t total, float cap, int dtype, b200_stream_t stream);
+/* Per token: q_out[row, h] = q_in[row, h] / rms * (1 + temp_coef ln(floor((pos + 1) / temp_every) + 1)) as fp32
+ * (temp_every 0: no temperature); with k_in / v_in (column blocks of the same matrix, row stride ld):
+ * k_cache[slot, g] = k_in[row, g] / rms and v_cache[slot] = v_in[row], or with v_other (row stride ld_other)
+ * (1 - lam) v_in[row] + lam v_other[row].  rms over the head's dim channels, eps inside the root. */
+B200_API int b200_sink_attn_prepare(float* q_out, const void* q_in, const void* k_in /*nullable*/,
+                                    const void* v_in /*nullable*/, int64_t ld, const void* v_other /*nullable*/,
+                                    int64_t ld_other, float lam, void* k_cache, void* v_cache,
+                                    const int32_t* positions, const int32_t* slots, int64_t rows, int64_t H, int64_t G,
+                                    int64_t dim, int64_t vdim, float eps, float temp_coef, int64_t temp_every,
+                                    int dtype, b200_stream_t stream);
+/* out[row, h] = sum_j p_j v_j over the cached rows j <= position i of the row (paged), p_j = exp(s_j) /
+ * (exp(sink[h]) + sum_j' exp(s_j')), s_j = scale q . k_j - r1[h] ln(1 + r2[h] (i - j)).  r1 / r2 (both or
+ * neither) and sink are fp32 [H], nullable.  q fp32 [rows, H, dim]; caches [slots, G, dim] and [slots, G, vdim]
+ * of type `dtype`; CUDA cores, any sizes. */
+B200_API int b200_sink_attn(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                            const float* r1 /*nullable*/, const float* r2 /*nullable*/,
+                            const float* sink /*nullable*/, const int32_t* q_cu_lens, const int32_t* kv_cu_lens,
+                            const int32_t* block_tables, const int32_t* cu_block_lens, const int32_t* token_seq,
+                            int64_t rows, int64_t H, int64_t G, int64_t dim, int64_t vdim, int64_t block_size,
+                            float scale, int dtype, b200_stream_t stream);
+/* The same for bf16 on the tensor cores, tiles of 16 consecutive tokens of a sequence: dim and vdim multiples of
+ * 16, at most 128 (..._supported tells); q_max: the longest portion of the step. */
+B200_API int b200_sink_attn_prefill_supported(int64_t dim, int64_t vdim, int dtype);
+B200_API int b200_sink_attn_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                                    const float* r1 /*nullable*/, const float* r2 /*nullable*/,
+                                    const float* sink /*nullable*/, const int32_t* q_cu_lens,
+                                    const int32_t* kv_cu_lens, const int32_t* block_tables,
+                                    const int32_t* cu_block_lens, int64_t n_seq, int64_t q_max, int64_t H, int64_t G,
+                                    int64_t dim, int64_t vdim, int64_t block_size, float scale, int dtype,
+                                    b200_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -103,9 +103,9 @@ SIGNATURES = {
     "b200_gated_act": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _int, _vp]),
     "b200_heads_to_rows": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _int, _vp]),
     "b200_latent_prepare": (_int, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32, _vp, _vp, _i64, _i64,
-                                   _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+                                   _i64, _i64, _i64, _i64, _f32, _int, _int, _vp]),
     "b200_latent_attn": (_int, [_vp, _i64, _i64, _vp, _i64, _i64, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
-                                _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp, _i64, _int, _vp]),
+                                _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _i64, _int, _vp, _i64, _int, _vp]),
     "b200_latent_attn_workspace_bytes": (_i64, [_i64, _i64, _i64, _i64]),
     "b200_delta_rule": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _vp, _vp, _vp, _vp, _vp,
                                _vp, _vp, _i64, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
@@ -116,7 +116,8 @@ SIGNATURES = {
     "b200_grouped_gemv": (_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64,
                                  _int, _vp]),
     "b200_moe_gather": (_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
-    "b200_moe_combine": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _int, _vp]),
+    "b200_moe_combine": (_int, [_vp, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
+    "b200_moe_table_route": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
     # post-norm residual with depth-weighted history, minimal gated recurrence, differential attention
     # (postnorm.cu, mingru.cu, diff_attn.cu)
     "b200_bigram_embed": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _f32, _int, _vp]),
@@ -145,6 +146,18 @@ SIGNATURES = {
                                         _vp]),
     "b200_diff_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                                       _i64, _i64, _i64, _f32, _i64, _i64, _f32, _f32, _f32, _int, _vp]),
+    # norm after the residual sum, logit cap, attention with a distance bias and a sink (postnorm.cu, sink_attn.cu)
+    "b200_sumnorm_residual": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _f32, _int, _vp]),
+    "b200_sumnorm_residual_splitk": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _f32, _int,
+                                            _vp]),
+    "b200_softcap": (_int, [_vp, _vp, _i64, _f32, _int, _vp]),
+    "b200_sink_attn_prepare": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _f32, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                      _i64, _i64, _f32, _f32, _i64, _int, _vp]),
+    "b200_sink_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                              _i64, _i64, _f32, _int, _vp]),
+    "b200_sink_attn_prefill_supported": (_int, [_i64, _i64, _int]),
+    "b200_sink_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
+                                      _i64, _i64, _i64, _i64, _f32, _int, _vp]),
 }
 
 # Which source files a partial library needs for a group of entry points.  The whole library
@@ -152,7 +165,7 @@ SIGNATURES = {
 # just the sources a model asks for into a library of its own.
 ALL_SOURCES = ("runtime.cu", "elementwise.cu", "sampling.cu", "paged_attn.cu", "prefill_attn.cu", "w4a16.cu",
                "dense.cu", "allreduce.cu", "hyper.cu", "latent_attn.cu", "delta_rule.cu", "moe.cu", "postnorm.cu", "mingru.cu",
-               "diff_attn.cu")
+               "diff_attn.cu", "sink_attn.cu")
 
 _lib: Optional[C.CDLL] = None
 _lib_sources: frozenset = frozenset()

@@ -9,8 +9,10 @@
 //
 //   latent_prepare : per token  c = rmsnorm(dkv[:rank]) * w -> cache ; kr = rope(dkv[rank:]) -> cache ;
 //                    rope on the rotary part of every query head in place.  Angles pos * f_i, cos
-//                    and sin in fp32; pairs are interleaved (2i, 2i+1); `mult` scales cos and sin.
-//   latent_attn    : causal softmax attention of packed query rows over the paged rows; scores,
+//                    and sin in fp32; pairs are interleaved (2i, 2i+1) or, with half_pairs, (i, i + dims/2);
+//                    `mult` scales cos and sin.
+//   latent_attn    : causal softmax attention of packed query rows over the paged rows (with window > 0
+//                    only over the last `window` keys, the row's own included); scores,
 //                    weights and accumulators in fp32.  One CTA per (token, group of 8 heads), one
 //                    warp per head, 32-key tiles staged once per CTA in shared memory.
 #include "common.cuh"
@@ -27,7 +29,7 @@ __global__ void latent_prepare_kernel(T* __restrict__ q, int64_t ldq, const T* _
                                       const float* __restrict__ cw, const float* __restrict__ inv_freq,
                                       float mult, const int* __restrict__ positions,
                                       const int* __restrict__ slots, int H, int dim, int rd, int dims,
-                                      int rank, float eps) {
+                                      int rank, float eps, int half_pairs) {
   extern __shared__ float cs[];  // [dims / 2] cos, [dims / 2] sin
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -54,15 +56,17 @@ __global__ void latent_prepare_kernel(T* __restrict__ q, int64_t ldq, const T* _
   for (int k = threadIdx.x; k < tasks; k += blockDim.x) {
     const int hh = k / np, i = k - hh * np;
     const float c = cs[i], s = cs[np + i];
+    // the partner of channel i: its neighbour (pairs 2i, 2i + 1) or the channel half the turned width on (i, i + np)
+    const int e0 = half_pairs ? i : 2 * i, e1 = half_pairs ? i + np : 2 * i + 1;
     if (hh < H) {
-      T* p = q + (size_t)row * ldq + (size_t)hh * (dim + rd) + dim + 2 * i;
-      const float u = Num<T>::to_f(p[0]), v = Num<T>::to_f(p[1]);
-      p[0] = Num<T>::from_f(u * c - v * s);
-      p[1] = Num<T>::from_f(v * c + u * s);
+      T* p = q + (size_t)row * ldq + (size_t)hh * (dim + rd) + dim;
+      const float u = Num<T>::to_f(p[e0]), v = Num<T>::to_f(p[e1]);
+      p[e0] = Num<T>::from_f(u * c - v * s);
+      p[e1] = Num<T>::from_f(v * c + u * s);
     } else {
-      const float u = Num<T>::to_f(src[rank + 2 * i]), v = Num<T>::to_f(src[rank + 2 * i + 1]);
-      dst[rank + 2 * i] = Num<T>::from_f(u * c - v * s);
-      dst[rank + 2 * i + 1] = Num<T>::from_f(v * c + u * s);
+      const float u = Num<T>::to_f(src[rank + e0]), v = Num<T>::to_f(src[rank + e1]);
+      dst[rank + e0] = Num<T>::from_f(u * c - v * s);
+      dst[rank + e1] = Num<T>::from_f(v * c + u * s);
     }
   }
 }
@@ -74,7 +78,7 @@ latent_attn_kernel(T* __restrict__ out, int64_t out_hs, int64_t out_ts, const QA
                    const T* __restrict__ cache, int64_t ldc, const int* __restrict__ q_cu,
                    const int* __restrict__ kv_cu, const int* __restrict__ tables,
                    const int* __restrict__ blk_cu, const int* __restrict__ token_seq, int H, int dim,
-                   int rd, int rank, int block_size, float scale) {
+                   int rd, int rank, int block_size, float scale, int window) {
   extern __shared__ float sm[];
   const int Dk = rank + rd, ldk = Dk + 1;
   float* qs = sm;                           // [kHeadsPerCta][Dk]
@@ -85,6 +89,7 @@ latent_attn_kernel(T* __restrict__ out, int64_t out_hs, int64_t out_ts, const QA
   const int seq = token_seq[row];
   const int q_len = q_cu[seq + 1] - q_cu[seq], kv_len = kv_cu[seq + 1] - kv_cu[seq];
   const int pos = kv_len - q_len + (row - q_cu[seq]);   // last visible key
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;   // first visible key
   const int* table = tables + blk_cu[seq];
   if (h < H) {
     const QA* a = qa + (size_t)h * qa_hs + (size_t)row * qa_ts;
@@ -96,12 +101,12 @@ latent_attn_kernel(T* __restrict__ out, int64_t out_hs, int64_t out_ts, const QA
 #pragma unroll
   for (int i = 0; i < NR; ++i) acc[i] = 0.0f;
   float m = -INFINITY, l = 0.0f;
-  for (int j0 = 0; j0 <= pos; j0 += kTileKeys) {
+  for (int j0 = lo / kTileKeys * kTileKeys; j0 <= pos; j0 += kTileKeys) {
     __syncthreads();   // previous tile fully consumed (and qs written, first time round)
     for (int jj = warp; jj < kTileKeys; jj += kHeadsPerCta) {
       const int key = j0 + jj;
       float* dstk = Ks + jj * ldk;
-      if (key <= pos) {
+      if (key <= pos && key >= lo) {
         const T* srck = cache + ((size_t)table[key / block_size] + key % block_size) * ldc;
         for (int d = lane; d < Dk; d += 32) dstk[d] = Num<T>::to_f(srck[d]);
       } else {
@@ -114,7 +119,7 @@ latent_attn_kernel(T* __restrict__ out, int64_t out_hs, int64_t out_ts, const QA
       const float* kj = Ks + lane * ldk;
       float s = 0.0f;
       for (int d = 0; d < Dk; ++d) s += qh[d] * kj[d];
-      s = (j0 + lane <= pos) ? s * scale : -INFINITY;
+      s = (j0 + lane <= pos && j0 + lane >= lo) ? s * scale : -INFINITY;
       float mx = s;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -152,7 +157,7 @@ int launch_latent_attn(void* out, int64_t out_hs, int64_t out_ts, const void* qa
                        int64_t qa_ts, const void* q, int64_t ldq, const void* cache, int64_t ldc,
                        const int* q_cu, const int* kv_cu, const int* tables, const int* blk_cu,
                        const int* token_seq, int64_t rows, int H, int dim, int rd, int rank,
-                       int block_size, float scale, cudaStream_t st) {
+                       int block_size, float scale, int window, cudaStream_t st) {
   const int Dk = rank + rd;
   const size_t smem = ((size_t)kHeadsPerCta * Dk + (size_t)kTileKeys * (Dk + 1)) * sizeof(float);
   B200_CHECK_ARG(smem <= 200 * 1024, "latent_attn: rank + rot_dim = %d does not fit in shared memory", Dk);
@@ -164,7 +169,7 @@ int launch_latent_attn(void* out, int64_t out_hs, int64_t out_ts, const void* qa
                                               static_cast<const QA*>(qa), qa_hs, qa_ts,
                                               static_cast<const T*>(q), ldq, static_cast<const T*>(cache),
                                               ldc, q_cu, kv_cu, tables, blk_cu, token_seq, H, dim, rd, rank,
-                                              block_size, scale);
+                                              block_size, scale, window);
   B200_LAUNCH_OK("latent_attn_kernel");
   return B200_OK;
 }
@@ -173,9 +178,9 @@ template <typename T, typename QA>
 int dispatch_nr(int rank, void* out, int64_t out_hs, int64_t out_ts, const void* qa, int64_t qa_hs,
                 int64_t qa_ts, const void* q, int64_t ldq, const void* cache, int64_t ldc, const int* q_cu,
                 const int* kv_cu, const int* tables, const int* blk_cu, const int* token_seq, int64_t rows,
-                int H, int dim, int rd, int block_size, float scale, cudaStream_t st) {
+                int H, int dim, int rd, int block_size, float scale, int window, cudaStream_t st) {
 #define LA_ARGS out, out_hs, out_ts, qa, qa_hs, qa_ts, q, ldq, cache, ldc, q_cu, kv_cu, tables, blk_cu, \
-                token_seq, rows, H, dim, rd, rank, block_size, scale, st
+                token_seq, rows, H, dim, rd, rank, block_size, scale, window, st
   const int nr = (rank + 31) / 32;
   if (nr <= 2) return launch_latent_attn<T, QA, 2>(LA_ARGS);
   if (nr <= 4) return launch_latent_attn<T, QA, 4>(LA_ARGS);
@@ -226,7 +231,7 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
                        const __nv_bfloat16* __restrict__ cache, int64_t ldc, const int* __restrict__ q_cu,
                        const int* __restrict__ kv_cu, const int* __restrict__ tables,
                        const int* __restrict__ blk_cu, const int* __restrict__ token_seq, int rows, int H,
-                       int dim, int rd, int rank, int block_size, float scale) {
+                       int dim, int rd, int rank, int block_size, float scale, int window) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int Dk = rank + rd, DkP = (Dk + 31) / 32 * 32, ld = DkP + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [16][ld]
@@ -241,6 +246,7 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
   const int seq = token_seq[row];
   const int q_len = q_cu[seq + 1] - q_cu[seq], kv_len = kv_cu[seq + 1] - kv_cu[seq];
   const int pos = kv_len - q_len + (row - q_cu[seq]);
+  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;   // first visible key
   const int* table = tables + blk_cu[seq];
   // stage Q: row r of the tile is head hg * 16 + r of this token: [folded query (rank) | rotary part (rd) | 0]
   for (int r = warp; r < kMmaRows; r += 4) {
@@ -256,9 +262,9 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
       Qs[r * ld + d] = __float2bfloat16_rn(v);
     }
   }
-  const int tiles_total = pos / kTileKeys + 1;
-  const int tps = (tiles_total + n_splits - 1) / n_splits;
-  const int tile0 = z * tps, tile1 = min(tiles_total, tile0 + tps);
+  const int tile_lo = lo / kTileKeys, tiles_total = pos / kTileKeys + 1;        // tiles tile_lo .. tiles_total - 1
+  const int tps = (tiles_total - tile_lo + n_splits - 1) / n_splits;
+  const int tile0 = tile_lo + z * tps, tile1 = min(tiles_total, tile0 + tps);
   float acc[NTV][4];
 #pragma unroll
   for (int i = 0; i < NTV; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
@@ -318,7 +324,7 @@ latent_attn_mma_kernel(__nv_bfloat16* __restrict__ out, int64_t out_hs, int64_t 
     float sv[4];
     {
       const int key = j0 + warp * 8 + 2 * t;
-      const bool v0 = key <= pos, v1 = key + 1 <= pos;
+      const bool v0 = key <= pos && key >= lo, v1 = key + 1 <= pos && key + 1 >= lo;
       const bool r0 = hg * kMmaRows + g < H, r1 = hg * kMmaRows + g + 8 < H;
       sv[0] = (v0 && r0) ? s[0] * scale : -INFINITY;
       sv[1] = (v1 && r0) ? s[1] * scale : -INFINITY;
@@ -467,7 +473,7 @@ int launch_latent_mma(void* out, int64_t out_hs, int64_t out_ts, float* o_part, 
                       const void* qa, int64_t qa_hs, int64_t qa_ts, const void* q, int64_t ldq,
                       const void* cache, int64_t ldc, const int* q_cu, const int* kv_cu, const int* tables,
                       const int* blk_cu, const int* token_seq, int64_t rows, int H, int dim, int rd, int rank,
-                      int block_size, float scale, cudaStream_t st) {
+                      int block_size, float scale, int window, cudaStream_t st) {
   const int DkP = (rank + rd + 31) / 32 * 32, ld = DkP + 8;
   const size_t smem = ((size_t)(kMmaRows + 2 * kTileKeys) * ld + 16 + 2 * kMmaRows * 40) * sizeof(__nv_bfloat16) +
                       2 * kMmaRows * 4 * sizeof(float);
@@ -479,7 +485,7 @@ int launch_latent_mma(void* out, int64_t out_hs, int64_t out_ts, float* o_part, 
   kern<<<grid, 128, smem, st>>>(static_cast<__nv_bfloat16*>(out), out_hs, out_ts, o_part, ml_part, n_splits,
                                 static_cast<const QA*>(qa), qa_hs, qa_ts, static_cast<const __nv_bfloat16*>(q), ldq,
                                 static_cast<const __nv_bfloat16*>(cache), ldc, q_cu, kv_cu, tables, blk_cu,
-                                token_seq, (int)rows, H, dim, rd, rank, block_size, scale);
+                                token_seq, (int)rows, H, dim, rd, rank, block_size, scale, window);
   B200_LAUNCH_OK("latent_attn_mma_kernel");
   if (n_splits > 1) {
     latent_combine_kernel<<<dim3((unsigned)rows, (unsigned)H), 128, 0, st>>>(
@@ -494,9 +500,9 @@ int dispatch_mma(int rank, void* out, int64_t out_hs, int64_t out_ts, float* o_p
                  const void* qa, int64_t qa_hs, int64_t qa_ts, const void* q, int64_t ldq, const void* cache,
                  int64_t ldc, const int* q_cu, const int* kv_cu, const int* tables, const int* blk_cu,
                  const int* token_seq, int64_t rows, int H, int dim, int rd, int block_size, float scale,
-                 cudaStream_t st) {
+                 int window, cudaStream_t st) {
 #define LM_ARGS out, out_hs, out_ts, o_part, ml_part, n_splits, qa, qa_hs, qa_ts, q, ldq, cache, ldc, q_cu, kv_cu, \
-                tables, blk_cu, token_seq, rows, H, dim, rd, rank, block_size, scale, st
+                tables, blk_cu, token_seq, rows, H, dim, rd, rank, block_size, scale, window, st
   const int need = (rank + 31) / 32;   // 8-column tiles per warp (4 warps share the latent columns)
   if (need <= 2) return launch_latent_mma<QA, 2>(LM_ARGS);
   if (need <= 4) return launch_latent_mma<QA, 4>(LM_ARGS);
@@ -517,7 +523,7 @@ extern "C" {
 int b200_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t ld_dkv, void* cache, int64_t ldc,
                         const float* c_norm_weight, const float* inv_freq, float mult,
                         const int32_t* positions, const int32_t* slots, int64_t rows, int64_t H,
-                        int64_t dim, int64_t rd, int64_t dims, int64_t rank, float eps, int dtype,
+                        int64_t dim, int64_t rd, int64_t dims, int64_t rank, float eps, int half_pairs, int dtype,
                         b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(q && dkv && cache && c_norm_weight && inv_freq && positions && slots,
@@ -531,7 +537,8 @@ int b200_latent_prepare(void* q, int64_t ldq, const void* dkv, int64_t ld_dkv, v
 #define LP_LAUNCH(T)                                                                                   \
   latent_prepare_kernel<T><<<(unsigned)rows, 128, smem, st>>>(                                          \
       static_cast<T*>(q), ldq, static_cast<const T*>(dkv), ld_dkv, static_cast<T*>(cache), ldc,          \
-      c_norm_weight, inv_freq, mult, positions, slots, (int)H, (int)dim, (int)rd, (int)dims, (int)rank, eps)
+      c_norm_weight, inv_freq, mult, positions, slots, (int)H, (int)dim, (int)rd, (int)dims, (int)rank, eps,   \
+      half_pairs)
   switch (dtype) {
     case B200_BF16: LP_LAUNCH(__nv_bfloat16); break;
     case B200_FP16: LP_LAUNCH(__half); break;
@@ -553,21 +560,21 @@ int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_strid
                      int64_t ldq, const void* cache, int64_t ldc, const int32_t* q_cu_lens,
                      const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
                      const int32_t* token_seq, int64_t rows, int64_t H, int64_t dim, int64_t rd,
-                     int64_t rank, int64_t block_size, float scale, int n_splits, void* workspace,
+                     int64_t rank, int64_t block_size, float scale, int64_t window, int n_splits, void* workspace,
                      int64_t workspace_bytes, int dtype, b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && q_absorbed && q && cache && q_cu_lens && kv_cu_lens && block_tables &&
                      cu_block_lens && token_seq,
                  "latent_attn: null pointer");
   B200_CHECK_ARG(rows > 0 && H > 0 && H <= 65535 * kHeadsPerCta && dim >= 0 && rd >= 0 && rank > 0 &&
-                     block_size > 0 && ldq >= H * (dim + rd) && ldc >= rank + rd,
+                     block_size > 0 && ldq >= H * (dim + rd) && ldc >= rank + rd && window >= 0 && window < (1ll << 31),
                  "latent_attn: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
 #define LA_CALL(T, QA)                                                                                  \
   return dispatch_nr<T, QA>((int)rank, out, out_head_stride, out_token_stride, q_absorbed, qa_head_stride, \
                             qa_token_stride, q, ldq, cache, ldc, q_cu_lens, kv_cu_lens, block_tables,    \
                             cu_block_lens, token_seq, rows, (int)H, (int)dim, (int)rd, (int)block_size,   \
-                            scale, st)
+                            scale, (int)window, st)
   if (dtype == B200_BF16 && n_splits >= 1) {   // tensor-core form
     B200_CHECK_ARG((rank + rd) % 8 == 0 && ldc % 8 == 0 && is_aligned(cache, 16),
                    "latent_attn: the tensor-core form needs 16-byte aligned cache rows (rank + rot_dim and the row "
@@ -585,11 +592,11 @@ int b200_latent_attn(void* out, int64_t out_head_stride, int64_t out_token_strid
       return dispatch_mma<float>((int)rank, out, out_head_stride, out_token_stride, o_part, ml_part, n_splits,
                                  q_absorbed, qa_head_stride, qa_token_stride, q, ldq, cache, ldc, q_cu_lens,
                                  kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H, (int)dim,
-                                 (int)rd, (int)block_size, scale, st);
+                                 (int)rd, (int)block_size, scale, (int)window, st);
     return dispatch_mma<__nv_bfloat16>((int)rank, out, out_head_stride, out_token_stride, o_part, ml_part,
                                        n_splits, q_absorbed, qa_head_stride, qa_token_stride, q, ldq, cache, ldc,
                                        q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H,
-                                       (int)dim, (int)rd, (int)block_size, scale, st);
+                                       (int)dim, (int)rd, (int)block_size, scale, (int)window, st);
   }
   switch (dtype) {
     case B200_BF16:

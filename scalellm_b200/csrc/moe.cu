@@ -246,15 +246,30 @@ __global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, i
   for (int i = threadIdx.x; i < W; i += blockDim.x) xs[(size_t)pos * W + i] = Num<T>::from_f(Num<T>::to_f(src[i]) * sc);
 }
 
+// out[row] = scale * sum_k Y[pos_of_pair[row, k]] (+ addend[row]: a result every token gets, a shared expert's)
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const T* __restrict__ Y, int64_t ldy,
-                                   const int* __restrict__ pos_of_pair, int W, int top) {
+                                   const int* __restrict__ pos_of_pair, int W, int top, float scale,
+                                   const T* __restrict__ addend, int64_t ld_add) {
   const int row = blockIdx.x;
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.0f;
     for (int k = 0; k < top; ++k)
       acc += Num<T>::to_f(Y[(size_t)pos_of_pair[(size_t)row * top + k] * ldy + i]);
+    acc *= scale;
+    if (addend) acc += Num<T>::to_f(addend[(size_t)row * ld_add + i]);
     out[(size_t)row * W + i] = Num<T>::from_f(acc);
+  }
+}
+
+// ids[row, k] = table[token of the row, k]: the experts of a token are a property of its id
+__global__ void moe_table_route_kernel(int* __restrict__ ids, const int* __restrict__ table,
+                                       const int* __restrict__ tokens, int64_t n, int top, int vocab, int E) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int tok = tokens[i / top];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    int e = table[(int64_t)tok * top + i % top];
+    ids[i] = e < 0 ? 0 : (e >= E ? E - 1 : e);
   }
 }
 
@@ -361,14 +376,32 @@ int b200_moe_gather(void* xs, const void* h, int64_t ldh, const int32_t* sorted_
 }
 
 int b200_moe_combine(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair, int64_t rows,
-                     int64_t W, int64_t top, int dtype, b200_stream_t stream) {
+                     int64_t W, int64_t top, float scale, const void* addend, int64_t ld_add, int dtype,
+                     b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && Y && pos_of_pair, "moe_combine: null pointer");
-  B200_CHECK_ARG(rows > 0 && W > 0 && ldy >= W && top >= 1, "moe_combine: bad shape");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldy >= W && top >= 1 && (!addend || ld_add >= W), "moe_combine: bad shape");
   auto st = static_cast<cudaStream_t>(stream);
   MOE_DISPATCH(dtype, (moe_combine_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
-                          static_cast<T*>(out), static_cast<const T*>(Y), ldy, pos_of_pair, (int)W, (int)top)));
+                          static_cast<T*>(out), static_cast<const T*>(Y), ldy, pos_of_pair, (int)W, (int)top, scale,
+                          static_cast<const T*>(addend), ld_add)));
   B200_LAUNCH_OK("moe_combine_kernel");
+  return B200_OK;
+}
+
+int b200_moe_table_route(int32_t* expert_ids, const int32_t* table, const int32_t* tokens, int64_t rows, int64_t top,
+                         int64_t vocab, int64_t E, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(expert_ids && table && tokens, "moe_table_route: null pointer");
+  B200_CHECK_ARG(rows > 0 && top >= 1 && top <= kMaxTop && vocab > 0 && E >= 1 && E <= kMaxExperts &&
+                     rows * top < (1ll << 31),
+                 "moe_table_route: bad shape");
+  const int64_t n = rows * top;
+  int64_t grid = (n + 255) / 256;
+  if (grid > 4096) grid = 4096;
+  moe_table_route_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      expert_ids, table, tokens, n, (int)top, (int)vocab, (int)E);
+  B200_LAUNCH_OK("moe_table_route_kernel");
   return B200_OK;
 }
 

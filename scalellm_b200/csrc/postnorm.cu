@@ -6,6 +6,9 @@
 //   postnorm  r = x + mult * y / sqrt(mean_g(y^2) + eps) * w     mean over the channel's group: the row is cut
 //             into `groups` equal consecutive parts, each with its own root mean square
 //   history   H[n - 1] = r ; x' = sum_{j < n} c[j] H[j]          (optional) the depth-weighted average
+//   sumnorm   x' = (a x + y) / sqrt(mean((a x + y)^2) + eps) * w   the norm taken AFTER the sum; w one number for the
+//             whole row or one per channel
+//   softcap   out = cap tanh(in / cap)
 //   glu       out = g sigmoid(slope g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit)
 //   token gate out = gelu_tanh(a) * table[tok, col0 + c]          a per-token learned vector gates a projection
 //
@@ -240,6 +243,68 @@ token_side_postnorm_kernel(float* __restrict__ x_out, T* __restrict__ h_out, con
   postnorm_tail<T>(x_out, h_out, x_in, y_s, r_s, w, row, W, groups, mult, eps, hist, hist_stride, n_hist, coef);
 }
 
+// The norm after the sum for one row whose sublayer result y_s [W] lies in shared memory: s = alpha x + y replaces
+// y_s, then x' = s / sqrt(mean(s^2) + eps) * w[i * w_stride] (w_stride 0: one gain for the row).
+template <typename T>
+__device__ __forceinline__ void sumnorm_tail(float* __restrict__ x_out, T* __restrict__ h_out,
+                                             const float* __restrict__ x_in, float* y_s, float* red,
+                                             const float* __restrict__ w, int w_stride, int row, int W, float alpha,
+                                             float eps) {
+  const size_t base = (size_t)row * W;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float s = alpha * x_in[base + i] + y_s[i];
+    y_s[i] = s;
+    ss += s * s;
+  }
+  ss = block_sum<kRowThreads>(ss, red);
+  const float r = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float v = y_s[i] * r * w[(size_t)i * w_stride];
+    x_out[base + i] = v;
+    if (h_out) h_out[base + i] = Num<T>::from_f(v);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+sumnorm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                        const T* __restrict__ y, int64_t ldy, const float* __restrict__ w, int w_stride, int W,
+                        float alpha, float eps) {
+  extern __shared__ __align__(16) float sm[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) sm[i] = Num<T>::to_f(y[(size_t)row * ldy + i]);
+  sumnorm_tail<T>(x_out, h_out, x_in, sm, red, w, w_stride, row, W, alpha, eps);   // each thread reads back its own
+}
+
+// The same launch fed by the split-K partials of the matrix product that made y (see postnorm_residual_splitk).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+sumnorm_residual_splitk_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                               const float* __restrict__ partials, W4Plan plan, int64_t slot_stride,
+                               const float* __restrict__ w, int w_stride, int W, float alpha, float eps) {
+  extern __shared__ __align__(16) float sm[];
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const float* prow = partials + (size_t)row * W;
+  for (int v = threadIdx.x; v < W / 8; v += kRowThreads) {
+    float a[8];
+    w4_sum_partials8(a, prow + v * 8, slot_stride, w4_contrib_col(plan, v * 8));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm[v * 8 + i] = rnd<T>(a[i]);
+  }
+  __syncthreads();
+  sumnorm_tail<T>(x_out, h_out, x_in, sm, red, w, w_stride, row, W, alpha, eps);
+}
+
+template <typename T>
+__global__ void softcap_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t total, float cap) {
+  const float inv = 1.0f / cap;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = Num<T>::from_f(cap * tanhf(Num<T>::to_f(in[i]) * inv));
+}
+
 // out = x / sqrt(mean_group(x^2) + eps) * w for fp32 rows x, written as T; one CTA per row
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
@@ -435,6 +500,60 @@ int b200_postnorm_residual_splitk(float* x_out, void* h_out, const float* x_in, 
         hist_stride, (int)n_hist, coef);
   });
   B200_LAUNCH_OK("postnorm_residual_splitk_kernel");
+  return B200_OK;
+}
+
+int b200_sumnorm_residual(float* x_out, void* h_out, const float* x_in, const void* y, int64_t ldy,
+                          const float* weight, int64_t weight_stride, int64_t rows, int64_t W, float alpha, float eps,
+                          int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(x_out && x_in && y && weight, "sumnorm_residual: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldy >= W && W * 4 <= 200 * 1024 && (weight_stride == 0 || weight_stride == 1),
+                 "sumnorm_residual: bad shape (at most ~50K channels; weight stride 0 or 1)");
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)W * sizeof(float);
+  POSTNORM_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(sumnorm_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    sumnorm_residual_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+        x_out, static_cast<T*>(h_out), x_in, static_cast<const T*>(y), ldy, weight, (int)weight_stride, (int)W, alpha,
+        eps);
+  });
+  B200_LAUNCH_OK("sumnorm_residual_kernel");
+  return B200_OK;
+}
+
+int b200_sumnorm_residual_splitk(float* x_out, void* h_out, const float* x_in, const float* partials, int64_t n_slots,
+                                 const int32_t* plan6, const float* weight, int64_t weight_stride, int64_t rows,
+                                 int64_t W, float alpha, float eps, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(x_out && x_in && partials && plan6 && weight, "sumnorm_residual_splitk: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && W % 8 == 0 && W * 4 <= 200 * 1024 && n_slots == plan6[4] &&
+                     n_slots <= W4_MAX_SLOTS && is_aligned(partials, 16) && (weight_stride == 0 || weight_stride == 1),
+                 "sumnorm_residual_splitk: bad shape, or the partials are not those of the given partition");
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)W * sizeof(float);
+  const W4Plan plan = plan_of(plan6);
+  POSTNORM_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(sumnorm_residual_splitk_kernel<T>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sumnorm_residual_splitk_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+        x_out, static_cast<T*>(h_out), x_in, partials, plan, rows * W, weight, (int)weight_stride, (int)W, alpha, eps);
+  });
+  B200_LAUNCH_OK("sumnorm_residual_splitk_kernel");
+  return B200_OK;
+}
+
+int b200_softcap(void* out, const void* in, int64_t total, float cap, int dtype, b200_stream_t stream) {
+  if (total == 0) return B200_OK;
+  B200_CHECK_ARG(out && in, "softcap: null pointer");
+  B200_CHECK_ARG(total > 0 && cap > 0.0f, "softcap: the cap is a positive number");
+  auto st = static_cast<cudaStream_t>(stream);
+  POSTNORM_DISPATCH(dtype, (softcap_kernel<T><<<ew_grid(total), 256, 0, st>>>(static_cast<T*>(out),
+                                                                              static_cast<const T*>(in), total, cap)));
+  B200_LAUNCH_OK("softcap_kernel");
   return B200_OK;
 }
 

@@ -61,7 +61,7 @@ tensor_map_encode_fn get_tensor_map_encode() {
 
 extern "C" {
 
-int b200_abi_version(void) { return 1; }
+int b200_abi_version(void) { return 2; }
 
 const char* b200_last_error(void) { return b200::g_err; }
 

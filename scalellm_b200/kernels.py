@@ -714,8 +714,10 @@ def heads_to_rows(x: torch.Tensor, gate: Optional[torch.Tensor]) -> torch.Tensor
 # ---------------------------------------------------------------------------
 def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_norm_weight: torch.Tensor,
                    inv_freq: torch.Tensor, mult: float, positions: torch.Tensor, slots: torch.Tensor,
-                   n_heads: int, dim: int, rot_dim: int, rot_dims: int, rank: int, eps: float) -> None:
-    """In place on q (rotary part of every head) and on the cache rows `slots` (latent + rotary key)."""
+                   n_heads: int, dim: int, rot_dim: int, rot_dims: int, rank: int, eps: float,
+                   half_pairs: bool = False) -> None:
+    """In place on q (rotary part of every head) and on the cache rows `slots` (latent + rotary key).
+    half_pairs: channel i turns with channel i + rot_dims / 2 instead of its neighbour."""
     _cuda(q, dkv, cache)
     _f32(c_norm_weight, inv_freq)
     _check_i32(positions, slots)
@@ -724,8 +726,8 @@ def latent_prepare(q: torch.Tensor, dkv: torch.Tensor, cache: torch.Tensor, c_no
     assert q.dtype == dkv.dtype == cache.dtype and inv_freq.numel() == rot_dims // 2
     check(_lib.load().b200_latent_prepare(_p(q), q.stride(0), _p(dkv), dkv.stride(0), _p(cache), cache.stride(0),
                                           _p(c_norm_weight), _p(inv_freq), mult, _p(positions), _p(slots),
-                                          q.shape[0], n_heads, dim, rot_dim, rot_dims, rank, eps, _dt(q),
-                                          _stream()))
+                                          q.shape[0], n_heads, dim, rot_dim, rot_dims, rank, eps,
+                                          1 if half_pairs else 0, _dt(q), _stream()))
 
 
 def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype, width: int, rank: int = 0) -> int:
@@ -742,17 +744,19 @@ def latent_attn_splits(rows: int, n_heads: int, kv_max: int, dtype: torch.dtype,
 def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, q_cu: torch.Tensor,
                 kv_cu: torch.Tensor, block_tables: torch.Tensor, cu_block_lens: torch.Tensor,
                 token_seq: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, block_size: int,
-                scale: float, kv_max: int = 0) -> torch.Tensor:
+                scale: float, kv_max: int = 0, window: int = 0) -> torch.Tensor:
     """q_absorbed [H, rows, rank] (fp32 or q's dtype), q [rows, >= H * (dim + rot_dim)] with the rotary
     parts already rotated; returns the attention-weighted latents [H, rows, rank] in q's dtype.
-    kv_max: the longest cached length of the step (a host number; it only steers the key split)."""
+    kv_max: the longest cached length of the step (a host number; it only steers the key split).
+    window > 0: a row sees only the last `window` keys, its own included."""
     _cuda(q_absorbed, q, cache)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
     rows = q.shape[0]
     assert q_absorbed.shape == (n_heads, rows, rank) and q_absorbed.stride(2) == 1
     assert q_absorbed.dtype in (torch.float32, q.dtype) and q.stride(1) == 1 and cache.dtype == q.dtype
     out = torch.empty((n_heads, rows, rank), dtype=q.dtype, device=q.device)
-    splits = latent_attn_splits(rows, n_heads, kv_max, q.dtype, rank + rot_dim, rank) if cache.stride(0) % 8 == 0 else 0
+    visible = min(kv_max, window) if window > 0 and kv_max > 0 else kv_max
+    splits = latent_attn_splits(rows, n_heads, visible, q.dtype, rank + rot_dim, rank) if cache.stride(0) % 8 == 0 else 0
     ws, ws_bytes = None, 0
     if splits > 1:
         ws_bytes = int(_lib.load().b200_latent_attn_workspace_bytes(rows, n_heads, rank, splits))
@@ -762,7 +766,7 @@ def latent_attn(q_absorbed: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
                                        1 if q_absorbed.dtype == torch.float32 else 0, _p(q), q.stride(0),
                                        _p(cache), cache.stride(0), _p(q_cu), _p(kv_cu), _p(block_tables),
                                        _p(cu_block_lens), _p(token_seq), rows, n_heads, dim, rot_dim, rank,
-                                       block_size, scale, splits, _p(ws), ws_bytes, _dt(q), _stream()))
+                                       block_size, scale, window, splits, _p(ws), ws_bytes, _dt(q), _stream()))
     return out
 
 
@@ -863,14 +867,28 @@ def grouped_gemm(a: torch.Tensor, weights: torch.Tensor, offsets: torch.Tensor, 
 _GEMV_ROWS = 256   # at most this many (token, choice) rows: the weight-streaming kernel
 
 
-def moe_combine(y: torch.Tensor, pos_of_pair: torch.Tensor, rows: int, top: int) -> torch.Tensor:
-    _cuda(y)
+def moe_combine(y: torch.Tensor, pos_of_pair: torch.Tensor, rows: int, top: int, scale: float = 1.0,
+                addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[row] = scale * (sum of the row's `top` expert results in y) (+ addend[row])."""
+    _cuda(y, addend)
     _check_i32(pos_of_pair)
     assert y.dim() == 2 and y.stride(1) == 1 and pos_of_pair.numel() == rows * top
+    assert addend is None or (addend.shape == (rows, y.shape[1]) and addend.stride(1) == 1 and addend.dtype == y.dtype)
     out = torch.empty((rows, y.shape[1]), dtype=y.dtype, device=y.device)
-    check(_lib.load().b200_moe_combine(_p(out), _p(y), y.stride(0), _p(pos_of_pair), rows, y.shape[1], top,
-                                       _dt(y), _stream()))
+    check(_lib.load().b200_moe_combine(_p(out), _p(y), y.stride(0), _p(pos_of_pair), rows, y.shape[1], top, scale,
+                                       _p(addend), addend.stride(0) if addend is not None else 0, _dt(y), _stream()))
     return out
+
+
+def moe_table_route(table: torch.Tensor, tokens: torch.Tensor, n_experts: int) -> torch.Tensor:
+    """Expert ids [rows, top] int32 read from a table [vocab, top] by token id."""
+    _cuda(table, tokens)
+    _check_i32(table, tokens)
+    assert table.dim() == 2
+    ids = torch.empty((tokens.numel(), table.shape[1]), dtype=torch.int32, device=table.device)
+    check(_lib.load().b200_moe_table_route(_p(ids), _p(table), _p(tokens), tokens.numel(), table.shape[1],
+                                           table.shape[0], n_experts, _stream()))
+    return ids
 
 
 # ---------------------------------------------------------------------------
@@ -1144,4 +1162,103 @@ def diff_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gat
                              _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
                              block_size, scale, window, keep_first, lam, out_scale, eps, _dt(k_cache),
                              _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# norm after the residual sum, logit cap (csrc/postnorm.cu)
+# ---------------------------------------------------------------------------
+def sumnorm_residual(x: torch.Tensor, y, weight: torch.Tensor, alpha: float, eps: float,
+                     dtype: Optional[torch.dtype] = None, x_out: Optional[torch.Tensor] = None):
+    """s = alpha x + y ; x_out (default: x, in place) = s / sqrt(mean(s^2) + eps) * weight, weight one number or one
+    per channel.  y: the sublayer's result [rows, W], or the split-K partials of the matrix product that makes it
+    (their sum is rounded to `dtype` first).  Returns (x_out, x_out as y's type or None when that is fp32)."""
+    partials = isinstance(y, W4Partials)
+    data = y.data if partials else y
+    _cuda(x, data, weight)
+    _f32(x, weight)
+    rows, W = x.shape
+    assert weight.numel() in (1, W)
+    out = x if x_out is None else x_out
+    _f32(out)
+    w_stride = 0 if weight.numel() == 1 and W != 1 else 1
+    lib = _lib.load()
+    if partials:
+        _f32(data)
+        assert data.shape[1:] == (rows, W) and dtype is not None
+        h = torch.empty((rows, W), dtype=dtype, device=x.device) if dtype != torch.float32 else None
+        check(lib.b200_sumnorm_residual_splitk(_p(out), _p(h), _p(x), _p(data), data.shape[0], splitk_plan(W, y.K),
+                                               _p(weight), w_stride, rows, W, alpha, eps, _DT[dtype], _stream()))
+        return out, h
+    assert data.shape == (rows, W) and data.stride(1) == 1
+    h = torch.empty((rows, W), dtype=data.dtype, device=x.device) if data.dtype != torch.float32 else None
+    check(lib.b200_sumnorm_residual(_p(out), _p(h), _p(x), _p(data), data.stride(0), _p(weight), w_stride, rows, W,
+                                    alpha, eps, _dt(data), _stream()))
+    return out, h
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place: x <- cap * tanh(x / cap)."""
+    _cuda(x)
+    assert x.is_contiguous()
+    check(_lib.load().b200_softcap(_p(x), _p(x), x.numel(), cap, _dt(x), _stream()))
+    return x
+
+
+# ---------------------------------------------------------------------------
+# attention with unit queries and keys, a distance bias and a sink (csrc/sink_attn.cu)
+# ---------------------------------------------------------------------------
+def sink_attn_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, v_other: Optional[torch.Tensor],
+                      lam: float, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
+                      slots: torch.Tensor, H: int, G: int, dim: int, vdim: int, eps: float, temp_coef: float = 0.0,
+                      temp_every: int = 0) -> torch.Tensor:
+    """Unit-length queries with their temperature, fp32 [rows, H, dim]; unit-length keys and the values (blended
+    with v_other where given: (1 - lam) v + lam v_other) go to the cache rows `slots`.  q_in, k_in, v_in: column
+    blocks of one projection matrix."""
+    _cuda(q_in, k_in, v_in, v_other, k_cache, v_cache)
+    _check_i32(positions, slots)
+    rows, ld = q_in.shape[0], q_in.stride(0)
+    assert q_in.stride(1) == 1 and q_in.shape[1] == H * dim
+    assert k_in.stride(0) == ld and v_in.stride(0) == ld and k_in.dtype == v_in.dtype == q_in.dtype
+    assert k_in.stride(1) == 1 and v_in.stride(1) == 1
+    assert k_cache.dtype == v_cache.dtype == q_in.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1:] == (G, dim) and v_cache.shape[1:] == (G, vdim)
+    assert v_other is None or (v_other.shape == (rows, G * vdim) and v_other.stride(1) == 1 and v_other.dtype == q_in.dtype)
+    q = torch.empty((rows, H, dim), dtype=torch.float32, device=q_in.device)
+    check(_lib.load().b200_sink_attn_prepare(_p(q), _p(q_in), _p(k_in), _p(v_in), ld, _p(v_other),
+                                             v_other.stride(0) if v_other is not None else 0, lam, _p(k_cache),
+                                             _p(v_cache), _p(positions), _p(slots), rows, H, G, dim, vdim, eps,
+                                             temp_coef, temp_every, _dt(q_in), _stream()))
+    return q
+
+
+# a step whose longest portion has at least this many tokens runs the tensor-core kernel (bf16, fitting head sizes)
+SINK_ATTN_PREFILL_MIN_ROWS = 4
+
+
+def sink_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, r1: Optional[torch.Tensor],
+              r2: Optional[torch.Tensor], sink: Optional[torch.Tensor], q_cu: torch.Tensor, kv_cu: torch.Tensor,
+              block_tables: torch.Tensor, cu_block_lens: torch.Tensor, token_seq: torch.Tensor, block_size: int,
+              scale: float, n_seq: int = 0, q_max: int = 0, kv_max: int = 0) -> torch.Tensor:
+    """[rows, H * vdim] in the cache's dtype: causal softmax attention with the score scale q . k - r1 ln(1 + r2
+    (i - j)) and exp(sink) added to the denominator (r1 / r2 / sink fp32 [H] or None).  With n_seq and q_max (the
+    step's sequence count and longest portion, host numbers) a step with prompt portions in bf16 runs on the tensor
+    cores where the head sizes allow it; fp32 and odd sizes run the CUDA-core kernel."""
+    _cuda(q, k_cache, v_cache, r1, r2, sink)
+    _f32(q, r1, r2, sink)
+    _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
+    rows, H, dim = q.shape
+    G, vdim = v_cache.shape[1], v_cache.shape[2]
+    out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
+    lib = _lib.load()
+    impl = os.environ.get("B200_SINK_ATTN_IMPL")      # "simt": CUDA cores throughout
+    if (n_seq > 0 and q_max >= SINK_ATTN_PREFILL_MIN_ROWS and impl != "simt"
+            and lib.b200_sink_attn_prefill_supported(dim, vdim, _dt(k_cache))):
+        check(lib.b200_sink_attn_prefill(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(r1), _p(r2), _p(sink),
+                                         _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens), n_seq, q_max, H, G,
+                                         dim, vdim, block_size, scale, _dt(k_cache), _stream()))
+        return out
+    check(lib.b200_sink_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(r1), _p(r2), _p(sink), _p(q_cu),
+                             _p(kv_cu), _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
+                             block_size, scale, _dt(k_cache), _stream()))
     return out

@@ -686,12 +686,15 @@ class LatentAttention:
         k_h = Uk_h c ; v_h = Uv_h c ; s = (q_h[:dim] . k_h + q_h[dim:] . kr) * scale ; causal softmax
         out = Wo (concat_h(sum_j p_j v_hj) (* sigmoid(Wg h) when there is an output gate))
     Only [c | kr] is cached (LatentKVCache).  The key map is folded into the query and the value map is
-    applied after the weighted sum of latents, so the attention kernel runs in the latent space."""
+    applied after the weighted sum of latents, so the attention kernel runs in the latent space.
+    window > 0: position i sees only the keys j with i - j < window.  half_pairs: the rotary turn pairs channel t
+    with channel t + rot_dims / 2 instead of its neighbour."""
 
     def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, dim: int, rot_dim: int, vdim: int, rank: int,
                  scale: float, inv_freq: torch.Tensor, rot_mult: float, rot_dims: int, eps: float,
-                 dtype: torch.dtype, device):
+                 dtype: torch.dtype, device, window: int = 0, half_pairs: bool = False):
         self.H, self.dim, self.rd, self.vd, self.rank = n_heads, dim, rot_dim, vdim, rank
+        self.window, self.half_pairs = window, half_pairs
         self.scale, self.rot_mult, self.rot_dims, self.eps, self.dtype = scale, rot_mult, rot_dims, eps, dtype
         self.inv_freq = inv_freq.to(torch.float32).to(device).contiguous()
         qw = n_heads * (dim + rot_dim)
@@ -711,12 +714,12 @@ class LatentAttention:
         proj = self.in_proj(h)
         q, dkv = proj[:, : self.q_end], proj[:, self.q_end: self.dkv_end]
         kernels.latent_prepare(q, dkv, cache.rows, self.c_norm, self.inv_freq, self.rot_mult, positions,
-                               params.new_cache_slots, H, dim, rd, self.rot_dims, rank, self.eps)
+                               params.new_cache_slots, H, dim, rd, self.rot_dims, rank, self.eps, self.half_pairs)
         qu = q.view(T, H, dim + rd)[:, :, :dim].transpose(0, 1)                 # [H, T, dim] (strided view)
         qa = torch.bmm(qu, self.uk)                                             # folded query [H, T, rank]
         lat = kernels.latent_attn(qa, q, cache.rows, params.q_cu_seq_lens, params.kv_cu_seq_lens,
                                   params.block_tables, params.cu_block_lens, params.token_seq, H, dim, rd, rank,
-                                  cache.block_size(), self.scale, params.kv_max_seq_len)
+                                  cache.block_size(), self.scale, params.kv_max_seq_len, self.window)
         o = torch.bmm(lat, self.uv_t)                                           # [H, T, vdim]
         o = kernels.heads_to_rows(o, proj[:, self.dkv_end:] if self.has_gate else None)
         return self.o_proj(o)
@@ -929,5 +932,96 @@ class TokenSideInput:
             return out, (hh if hh is not None else out)
         y = self.proj(kernels.token_gated_gelu(self.gate(h), self.table, self.col0, tokens))
         return n(x, y, x_out=x_out, hist=hist, n_hist=n_hist, coef=coef)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# Layers of decoders that normalise after the residual sum with one gain per norm, attend with unit-length queries
+# and keys under a distance bias and a sink, and choose experts by the token id.
+# ---------------------------------------------------------------------------
+class SumNormResidual:
+    """x <- (alpha x + y) / rms(alpha x + y) * w on an fp32 residual x: the sublayer reads x itself and the norm
+    follows the sum.  w: one number for all channels, or one per channel."""
+
+    def __init__(self, weight: torch.Tensor, alpha: float, eps: float):
+        self.weight = weight.to(torch.float32).reshape(-1).contiguous()
+        self.alpha, self.eps = alpha, eps
+
+    def forward(self, x: torch.Tensor, y, dtype: torch.dtype, x_out: Optional[torch.Tensor] = None):
+        """y: the sublayer's result, or the split-K partials of the product that makes it (Linear.forward_fusable).
+        Returns (new x fp32, the same rows in `dtype` for the next matrix product — x itself in fp32)."""
+        out, h = kernels.sumnorm_residual(x, y, self.weight, self.alpha, self.eps, dtype, x_out)
+        return out, (h if h is not None else out)
+
+    __call__ = forward
+
+
+class SinkAttention:
+    """Causal softmax attention (csrc/sink_attn.cu) whose queries and keys are divided by their root mean square per
+    head (no weight), with
+        a query temperature  q_i *= 1 + temp_coef ln(floor((i + 1) / temp_every) + 1)        (temp_every 0: none)
+        a distance bias      s_ij = scale q_i . k_j - r1_h ln(1 + r2_h (i - j))               ("r1", "r2" [H], optional)
+        a sink               exp(sink_h) joins the softmax denominator, with no value         ("sink" [H], optional)
+    and H / G query heads per key/value head.  With mix_values the layer blends its values with those that another
+    layer made of the same tokens, v <- (1 - lam) v + lam v_other, before caching them; `lam` is this layer's
+    number.  No rotary turn: positions enter through the temperature and the bias only."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 temp_coef: float, temp_every: int, lam: Optional[float], eps: float, dtype: torch.dtype, device):
+        self.H, self.G, self.dim, self.vd = n_heads, n_kv_heads, dim, vdim
+        self.scale, self.temp_coef, self.temp_every, self.lam = scale, temp_coef, temp_every, lam
+        self.eps, self.dtype = eps, dtype
+        self.in_proj = Linear(torch.cat([w["q"], w["k"], w["v"]], dim=0))       # one GEMM for everything that reads h
+        self.q_end = n_heads * dim
+        self.k_end = self.q_end + n_kv_heads * dim
+        self.v_end = self.k_end + n_kv_heads * vdim
+        f = lambda name: w[name].to(torch.float32).to(device).contiguous() if name in w else None
+        self.r1, self.r2, self.sink = f("r1"), f("r2"), f("sink")
+        if (self.r1 is None) != (self.r2 is None):
+            raise ValueError("the distance bias takes both r1 and r2")
+        self.o_proj = Linear(w["o"])
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters,
+                v_other: Optional[torch.Tensor] = None):
+        """Returns (the mixer's result or its split-K partials, this layer's own unblended values of the step's rows
+        [rows, G * vdim]: what a later layer may blend into its own)."""
+        proj = self.in_proj(h)
+        v_in = proj[:, self.k_end: self.v_end]
+        blend = v_other if self.lam is not None else None
+        q = kernels.sink_attn_prepare(proj[:, : self.q_end], proj[:, self.q_end: self.k_end], v_in, blend,
+                                      self.lam if blend is not None else 0.0, cache.key_cache, cache.value_cache,
+                                      positions, params.new_cache_slots, self.H, self.G, self.dim, self.vd, self.eps,
+                                      self.temp_coef, self.temp_every)
+        o = kernels.sink_attn(q, cache.key_cache, cache.value_cache, self.r1, self.r2, self.sink,
+                              params.q_cu_seq_lens, params.kv_cu_seq_lens, params.block_tables, params.cu_block_lens,
+                              params.token_seq, cache.block_size(), self.scale, params.num_sequences,
+                              params.q_max_seq_len, params.kv_max_seq_len)
+        return self.o_proj.forward_fusable(o), v_in
+
+    __call__ = forward
+
+
+class TableMoE:
+    """Experts chosen by the token id: row `tok` of an integer table [vocab, top] names the token's experts, each
+    weighted 1 / top:   out = (1 / top) sum_e down_e(act(gate_e h) * (up_e h))  (+ shared(h), an expert that every
+    token uses).  Expert weights are stacked [E, ...]; pairs are grouped by expert on the device (no host sync)."""
+
+    def __init__(self, table: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, act: str,
+                 shared: Optional["GatedMLP"] = None):
+        self.table = table.to(torch.int32).contiguous()
+        self.gate_up = torch.cat([gate, up], dim=1).contiguous()     # [E, 2 ff, W]
+        self.down = down.contiguous()                                  # [E, W, ff]
+        self.E, self.top, self.act, self.shared = gate.shape[0], self.table.shape[1], act, shared
+
+    def forward(self, h: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+        rows = h.shape[0]
+        ids = kernels.moe_table_route(self.table, tokens, self.E)
+        offsets, sorted_pair, pos_of_pair = kernels.moe_plan(ids, self.E)
+        n = rows * self.top
+        gu = kernels.grouped_gemm(h, self.gate_up, offsets, n, sorted_pair, None, self.top)
+        y = kernels.grouped_gemm(kernels.gated_act(gu, self.act), self.down, offsets, n)
+        return kernels.moe_combine(y, pos_of_pair, rows, self.top, 1.0 / self.top,
+                                   self.shared(h) if self.shared is not None else None)
 
     __call__ = forward
