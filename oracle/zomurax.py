@@ -60,6 +60,28 @@ def query_temperature(pos: torch.Tensor, q_temp: Optional[dict]) -> torch.Tensor
     return 1.0 + float(q_temp["coef"]) * torch.log(steps + 1.0)
 
 
+def sink_attend(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, pos: torch.Tensor, scale: float,
+                r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """q [T, H, dim] at positions pos over the keys K [n, G, dim] and values V [n, G, vd] of positions 0 .. n - 1."""
+    T, H, G = q.shape[0], q.shape[1], K.shape[1]
+    out = torch.zeros(T, H, V.shape[2], dtype=q.dtype)
+    for t in range(T):
+        i = int(pos[t])
+        dist = torch.arange(i, -1, -1, dtype=q.dtype)          # i - j for j = 0 .. i
+        for hh in range(H):
+            g = hh // (H // G)
+            s = (K[: i + 1, g] @ q[t, hh]) * scale
+            if r1 is not None:
+                s = s - r1[hh] * torch.log(1.0 + r2[hh] * dist)
+            mx = s.max()
+            e = torch.exp(s - mx)
+            den = e.sum()
+            if sink is not None:
+                den = den + torch.exp(sink[hh] - mx)
+            out[t, hh] = (e / den) @ V[: i + 1, g]
+    return out
+
+
 def sink_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float, st: dict,
                    shared_v: dict, first_of_shared: bool) -> torch.Tensor:
     """st: this layer's cached keys and values of the sequence; shared_v: where the first value-sharing layer leaves
@@ -79,22 +101,29 @@ def sink_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, torch.Tensor
     K = torch.cat([st["k"], k]) if "k" in st else k
     V = torch.cat([st["v"], v]) if "v" in st else v
     st["k"], st["v"] = K, V
-    out = torch.zeros(T, H, vd, dtype=h.dtype)
+    out = sink_attend(q, K, V, pos, float(m["scale"]), w.get("r1"), w.get("r2"), w.get("sink"))
+    return out.reshape(T, H * vd) @ w["o"].T
+
+
+def window_visible(i: int, j: int, window: int) -> bool:
+    return j <= i and (window <= 0 or i - j < window)
+
+
+def latent_attend(q: torch.Tensor, C: torch.Tensor, KR: torch.Tensor, uk: torch.Tensor, uv: torch.Tensor,
+                  pos: torch.Tensor, scale: float, window: int) -> torch.Tensor:
+    """q [T, H, dim + rd] (turned) over latents C [n, rank] and turned shared key parts KR [n, rd];
+    uk [H, dim, rank], uv [H, vd, rank]."""
+    T, H = q.shape[0], q.shape[1]
+    out = torch.zeros(T, H, uv.shape[1], dtype=q.dtype)
     for t in range(T):
         i = int(pos[t])
-        dist = torch.arange(i, -1, -1, dtype=h.dtype)          # i - j for j = 0 .. i
+        js = [j for j in range(i + 1) if window_visible(i, j, window)]
+        cj, krj = C[js], KR[js]
         for hh in range(H):
-            g = hh // (H // G)
-            s = (K[: i + 1, g] @ q[t, hh]) * float(m["scale"])
-            if "r1" in w:
-                s = s - w["r1"][hh] * torch.log(1.0 + w["r2"][hh] * dist)
-            mx = s.max()
-            e = torch.exp(s - mx)
-            den = e.sum()
-            if "sink" in w:
-                den = den + torch.exp(w["sink"][hh] - mx)
-            out[t, hh] = (e / den) @ V[: i + 1, g]
-    return out.reshape(T, H * vd) @ w["o"].T
+            kk = torch.cat([cj @ uk[hh].T, krj], dim=-1)           # [keys, dim + rd]
+            p = torch.softmax((kk @ q[t, hh]) * scale, dim=0)
+            out[t, hh] = p @ (cj @ uv[hh].T)
+    return out
 
 
 def latent_window_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, torch.Tensor], m: dict, eps: float,
@@ -110,16 +139,8 @@ def latent_window_attention(h: torch.Tensor, pos: torch.Tensor, w: Dict[str, tor
     KR = torch.cat([st["kr"], kr]) if "kr" in st else kr
     st["c"], st["kr"] = C, KR
     window = int((m.get("mask") or {}).get("size", 0))
-    uk, uv = w["uk"].reshape(H, dim, rank), w["uv"].reshape(H, vd, rank)
-    out = torch.zeros(T, H, vd, dtype=h.dtype)
-    for t in range(T):
-        i = int(pos[t])
-        lo = max(0, i - window + 1) if window > 0 else 0
-        cj, krj = C[lo: i + 1], KR[lo: i + 1]
-        for hh in range(H):
-            kk = torch.cat([cj @ uk[hh].T, krj], dim=-1)           # [keys, dim + rd]
-            p = torch.softmax((kk @ q[t, hh]) * float(m["scale"]), dim=0)
-            out[t, hh] = p @ (cj @ uv[hh].T)
+    out = latent_attend(q, C, KR, w["uk"].reshape(H, dim, rank), w["uv"].reshape(H, vd, rank), pos, float(m["scale"]),
+                        window)
     return out.reshape(T, H * vd) @ w["o"].T
 
 
