@@ -716,6 +716,19 @@ B200_API int b200_sink_attn_prefill(void* out, int64_t ldo, const float* q, cons
                                     int64_t dim, int64_t vdim, int64_t block_size, float scale, int dtype,
                                     b200_stream_t stream);
 
+/* Single tokens in bf16 on the tensor cores: the 16 rows of a tile are the query heads of one key/value group, so
+ * the group's keys are read once for all of them (same head sizes as ..._prefill_supported).  n_splits > 1: every
+ * row's keys are shared out over that many CTAs and merged by a second kernel through the workspace (fp32, rows * H *
+ * n_splits * (2 + vdim) floats). */
+B200_API int b200_sink_attn_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                                      const float* r1 /*nullable*/, const float* r2 /*nullable*/,
+                                      const float* sink /*nullable*/, const int32_t* q_cu_lens,
+                                      const int32_t* kv_cu_lens, const int32_t* block_tables,
+                                      const int32_t* cu_block_lens, const int32_t* token_seq, int64_t rows, int64_t H,
+                                      int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale,
+                                      int64_t n_splits, float* workspace /*nullable*/, int64_t workspace_floats,
+                                      int dtype, b200_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

@@ -156,6 +156,8 @@ SIGNATURES = {
     "b200_sink_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                               _i64, _i64, _f32, _int, _vp]),
     "b200_sink_attn_prefill_supported": (_int, [_i64, _i64, _int]),
+    "b200_sink_attn_decode_tc": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                        _i64, _i64, _i64, _i64, _f32, _i64, _vp, _i64, _int, _vp]),
     "b200_sink_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                       _i64, _i64, _i64, _i64, _f32, _int, _vp]),
 }

@@ -467,6 +467,279 @@ int launch_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, 
   return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Single tokens in bf16 on the tensor cores: the 16 rows of the product are the query HEADS of one key/value group
+// (all at the row's position), so one pass over the group's keys serves every head that shares them.  One CTA per
+// (row, group[, chunk of 16 heads]); tiles of 64 keys are staged as above and each of the 4 warps takes 16 keys of
+// every tile with accumulators of its own; the warps' running maxima, sums and weighted sums are merged through
+// shared memory at the end.  A row's tiles may be shared out over n_splits such CTAs (few rows, many SMs): each then
+// hands its merged sums to sink_attn_merge_kernel through a workspace; the sink joins the sum at the very end.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kDK = 64;
+
+template <int KS_MAX, int VT_MAX>
+__global__ void __launch_bounds__(128)
+sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
+                           const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                           const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink,
+                           const int* __restrict__ q_cu, const int* __restrict__ kv_cu,
+                           const int* __restrict__ block_tables, const int* __restrict__ cu_block_lens,
+                           const int* __restrict__ token_seq, int H, int G, int dim, int vdim, int block_size,
+                           float scale, int n_splits, float* __restrict__ ws) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int KROW = dim + 8, VROW = vdim + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [16][KROW]
+  float* ml_s = reinterpret_cast<float*>(Qs + 16 * KROW);          // [4 warps][2: m, l][16 rows]
+  float* b_s = ml_s + 4 * 2 * 16;                                  // [2: r1, r2][16 rows]
+  unsigned char* big = reinterpret_cast<unsigned char*>(b_s + 2 * 16);
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [2][kDK][KROW]
+  __nv_bfloat16* Vs = Ks + 2 * kDK * KROW;                         // [2][kDK][VROW]
+  float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][16][vdim]
+  const int row = blockIdx.x / n_splits, split = blockIdx.x % n_splits, g = blockIdx.y, warp = threadIdx.x >> 5,
+            lane = threadIdx.x & 31;
+  const int R = H / G, h_base = blockIdx.z * 16;
+  const int n_heads = R - h_base < 16 ? R - h_base : 16;           // valid rows of the tile
+  const int seq = token_seq[row];
+  const int kv_len = kv_cu[seq + 1] - kv_cu[seq], q_len = q_cu[seq + 1] - q_cu[seq];
+  const int i = kv_len - q_len + (row - q_cu[seq]);
+  const int KS = dim / 16, VT = vdim / 16;
+  const int* table = block_tables + cu_block_lens[seq];
+  for (int e = threadIdx.x; e < 16 * dim; e += 128) {
+    const int rr = e / dim, d = e - rr * dim;
+    const float v = rr < n_heads ? q[((size_t)row * H + g * R + h_base + rr) * dim + d] : 0.0f;
+    Qs[rr * KROW + d] = __float2bfloat16_rn(v);
+  }
+  const bool biased = r1 != nullptr;
+  if (threadIdx.x < 16) {
+    const bool ok = biased && threadIdx.x < n_heads;
+    b_s[threadIdx.x] = ok ? r1[g * R + h_base + threadIdx.x] : 0.0f;
+    b_s[16 + threadIdx.x] = ok ? r2[g * R + h_base + threadIdx.x] : 0.0f;
+  }
+  const int all_tiles = i / kDK + 1;
+  // this CTA's share of the row's tiles (n_splits CTAs per row; an empty share hands on sums of zero)
+  const int per = (all_tiles + n_splits - 1) / n_splits;
+  const int tile0 = split * per;
+  const int n_tiles = all_tiles - tile0 < per ? (all_tiles - tile0 > 0 ? all_tiles - tile0 : 0) : per;
+  const size_t k_stride = (size_t)G * dim, v_stride = (size_t)G * vdim;
+  auto load_tile = [&](int idx, int buf) {
+    const int j0 = (tile0 + idx) * kDK;
+    const int sub = threadIdx.x & 1;
+    for (int key = threadIdx.x >> 1; key < kDK; key += 64) {
+      const int j = j0 + key;
+      const bool ok = j <= i;
+      size_t slot = 0;
+      if (ok) slot = (size_t)table[j / block_size] + j % block_size;
+      const __nv_bfloat16* kr = k_cache + slot * k_stride + (size_t)g * dim;
+      const __nv_bfloat16* vr = v_cache + slot * v_stride + (size_t)g * vdim;
+      __nv_bfloat16* kd = Ks + ((size_t)buf * kDK + key) * KROW;
+      __nv_bfloat16* vd = Vs + ((size_t)buf * kDK + key) * VROW;
+      for (int c = sub; c < dim / 8; c += 2) cp_async16(kd + c * 8, kr + c * 8, ok);
+      for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
+    }
+  };
+  if (n_tiles > 0) load_tile(0, 0);
+  cp_async_commit();
+  const int gr = lane >> 2, qc = (lane & 3) * 2;
+  float mx[2] = {-INFINITY, -INFINITY}, ls[2] = {0.0f, 0.0f};
+  float o[VT_MAX * 2][4];
+#pragma unroll
+  for (int n = 0; n < VT_MAX * 2; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+  float hb1[2] = {0.0f, 0.0f}, hb2[2] = {0.0f, 0.0f};   // the bias numbers of this lane's two heads
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = it & 1;
+    cp_async_wait_all();                                   // tile `it` has landed
+    __syncthreads();                                       // and everyone is done with tile it - 1 (and Qs, b_s stand)
+    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    cp_async_commit();
+    if (it == 0) { hb1[0] = b_s[gr]; hb1[1] = b_s[gr + 8]; hb2[0] = b_s[16 + gr]; hb2[1] = b_s[16 + gr + 8]; }
+    const int j0 = (tile0 + it) * kDK + warp * 16;       // this warp's 16 keys of the tile
+    if (j0 > i) continue;                                // all after the row's position
+    const __nv_bfloat16* kt = Ks + ((size_t)buf * kDK + warp * 16) * KROW;
+    const __nv_bfloat16* vt = Vs + ((size_t)buf * kDK + warp * 16) * VROW;
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KS_MAX; ++ks) {
+      if (ks < KS) {
+        uint32_t a[4], b[4];
+        ldsm_x4(a, Qs + (lane & 15) * KROW + ks * 16 + (lane >> 4) * 8);
+        ldsm_x4(b, kt + ((lane & 7) + (lane >> 4) * 8) * KROW + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16(sc[0], a, b[0], b[1]);
+        mma_bf16(sc[1], a, b[2], b[3]);
+      }
+    }
+    float rmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + n * 8 + qc + (e & 1);
+        float v = sc[n][e] * scale;
+        if (biased) v -= hb1[e >> 1] * __logf(1.0f + hb2[e >> 1] * (float)(i - j));
+        if (j > i) v = -INFINITY;
+        sc[n][e] = v;
+        rmax[e >> 1] = fmaxf(rmax[e >> 1], v);
+      }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r2i = 0; r2i < 2; ++r2i) {
+      rmax[r2i] = fmaxf(rmax[r2i], __shfl_xor_sync(0xffffffffu, rmax[r2i], 1));
+      rmax[r2i] = fmaxf(rmax[r2i], __shfl_xor_sync(0xffffffffu, rmax[r2i], 2));
+      const float nm = fmaxf(mx[r2i], rmax[r2i]);
+      msafe[r2i] = nm == -INFINITY ? 0.0f : nm;
+      corr[r2i] = __expf(mx[r2i] - msafe[r2i]);
+      mx[r2i] = nm;
+      ls[r2i] *= corr[r2i];
+    }
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+      for (int n = 0; n < VT_MAX * 2; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+    }
+    uint32_t phi[4], plo[4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const float p0 = __expf(sc[n][0] - msafe[0]), p1 = __expf(sc[n][1] - msafe[0]);
+      const float p2 = __expf(sc[n][2] - msafe[1]), p3 = __expf(sc[n][3] - msafe[1]);
+      ls[0] += p0 + p1;
+      ls[1] += p2 + p3;
+      split_bf16(p0, p1, phi[n * 2], plo[n * 2]);
+      split_bf16(p2, p3, phi[n * 2 + 1], plo[n * 2 + 1]);
+    }
+#pragma unroll
+    for (int vt16 = 0; vt16 < VT_MAX; ++vt16) {
+      if (vt16 < VT) {
+        uint32_t b[4];
+        ldsm_x4_t(b, vt + ((lane & 7) + ((lane >> 3) & 1) * 8) * VROW + vt16 * 16 + (lane >> 4) * 8);
+        mma_bf16(o[vt16 * 2], phi, b[0], b[1]);
+        mma_bf16(o[vt16 * 2 + 1], phi, b[2], b[3]);
+        mma_bf16(o[vt16 * 2], plo, b[0], b[1]);
+        mma_bf16(o[vt16 * 2 + 1], plo, b[2], b[3]);
+      }
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();                                       // the tiles are done with: their memory takes the partial sums
+#pragma unroll
+  for (int r2i = 0; r2i < 2; ++r2i) {
+    ls[r2i] += __shfl_xor_sync(0xffffffffu, ls[r2i], 1);
+    ls[r2i] += __shfl_xor_sync(0xffffffffu, ls[r2i], 2);
+    if ((lane & 3) == 0) {
+      ml_s[(warp * 2 + 0) * 16 + gr + r2i * 8] = mx[r2i];
+      ml_s[(warp * 2 + 1) * 16 + gr + r2i * 8] = ls[r2i];
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < VT_MAX * 2; ++n)
+    if (n < VT * 2) {
+      float* dst = o_s + ((size_t)warp * 16) * vdim + n * 8 + qc;
+      dst[(size_t)gr * vdim] = o[n][0];
+      dst[(size_t)gr * vdim + 1] = o[n][1];
+      dst[(size_t)(gr + 8) * vdim] = o[n][2];
+      dst[(size_t)(gr + 8) * vdim + 1] = o[n][3];
+    }
+  __syncthreads();
+  // warp w finishes heads w, w + 4, ...: lanes over the value channels
+  for (int rr = warp; rr < n_heads; rr += 4) {
+    float M = -INFINITY, L = 0.0f, f[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, ml_s[(w * 2 + 0) * 16 + rr]);
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float lw = ml_s[(w * 2 + 1) * 16 + rr];
+      f[w] = lw > 0.0f ? expf(ml_s[(w * 2 + 0) * 16 + rr] - M) : 0.0f;
+      L += f[w] * lw;
+    }
+    const int h = g * R + h_base + rr;
+    float x[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {                        // vdim <= 128: up to 4 channels per lane
+      const int col = lane + 32 * c;
+      x[c] = 0.0f;
+      if (col < vdim) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) x[c] += f[w] * o_s[((size_t)w * 16 + rr) * vdim + col];
+      }
+    }
+    if (ws) {
+      // one of several CTAs of this row: hand on (M, L) and the unnormalised sum; the merge kernel ends
+      float* dst = ws + (((size_t)row * H + h) * n_splits + split) * (size_t)(2 + vdim);
+      if (lane == 0) { dst[0] = M; dst[1] = L; }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (lane + 32 * c < vdim) dst[2 + lane + 32 * c] = x[c];
+      continue;
+    }
+    const float fo = sink_scale(M, L, sink, h);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int col = lane + 32 * c;
+      if (col < vdim) out[(size_t)row * ldo + (size_t)h * vdim + col] = __float2bfloat16_rn(x[c] * fo);
+    }
+  }
+}
+
+// The end of the walk for rows whose keys were shared out over n_splits CTAs: one warp per (row, head) merges the
+// shares' maxima, sums and weighted sums and lets the sink into the denominator.
+__global__ void __launch_bounds__(128)
+sink_attn_merge_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ ws,
+                       const float* __restrict__ sink, int64_t n_pairs, int H, int vdim, int n_splits) {
+  const int64_t pair = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);      // row * H + head
+  const int lane = threadIdx.x & 31;
+  if (pair >= n_pairs) return;
+  const int64_t row = pair / H;
+  const int h = (int)(pair - row * H);
+  const size_t stride = (size_t)(2 + vdim);
+  const float* src = ws + (size_t)pair * n_splits * stride;
+  float M = -INFINITY, L = 0.0f;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, src[s * stride]);
+  float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int s = 0; s < n_splits; ++s) {
+    const float* p = src + s * stride;
+    const float f = p[1] > 0.0f ? expf(p[0] - M) : 0.0f;
+    L += f * p[1];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      if (lane + 32 * c < vdim) x[c] += f * p[2 + lane + 32 * c];
+  }
+  const float fo = sink_scale(M, L, sink, h);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int col = lane + 32 * c;
+    if (col < vdim) out[row * ldo + (size_t)h * vdim + col] = __float2bfloat16_rn(x[c] * fo);
+  }
+}
+
+template <int KS_MAX, int VT_MAX>
+int launch_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache, const float* r1,
+                     const float* r2, const float* sink, const int* q_cu, const int* kv_cu, const int* tables,
+                     const int* blk_cu, const int* token_seq, int64_t rows, int H, int G, int dim, int vdim,
+                     int block_size, float scale, int n_splits, float* ws, cudaStream_t st) {
+  const int R = H / G;
+  const size_t tiles = ((size_t)2 * kDK * (dim + 8) + (size_t)2 * kDK * (vdim + 8)) * sizeof(__nv_bfloat16);
+  const size_t sums = (size_t)4 * 16 * vdim * sizeof(float);
+  const size_t smem = (size_t)16 * (dim + 8) * sizeof(__nv_bfloat16) + (4 * 2 * 16 + 2 * 16) * sizeof(float) +
+                      (tiles > sums ? tiles : sums);
+  auto kern = sink_attn_decode_tc_kernel<KS_MAX, VT_MAX>;
+  if (smem > 48 * 1024)
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((unsigned)(rows * n_splits), (unsigned)G, (unsigned)((R + 15) / 16));
+  kern<<<grid, 128, smem, st>>>(static_cast<__nv_bfloat16*>(out), ldo, q, static_cast<const __nv_bfloat16*>(k_cache),
+                                static_cast<const __nv_bfloat16*>(v_cache), r1, r2, sink, q_cu, kv_cu, tables, blk_cu,
+                                token_seq, H, G, dim, vdim, block_size, scale, n_splits, n_splits > 1 ? ws : nullptr);
+  B200_LAUNCH_OK("sink_attn_decode_tc_kernel");
+  if (n_splits > 1) {
+    const int64_t n_pairs = rows * H;
+    sink_attn_merge_kernel<<<(unsigned)((n_pairs + 3) / 4), 128, 0, st>>>(static_cast<__nv_bfloat16*>(out), ldo, ws,
+                                                                          sink, n_pairs, H, vdim, n_splits);
+    B200_LAUNCH_OK("sink_attn_merge_kernel");
+  }
+  return B200_OK;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -554,6 +827,31 @@ int b200_sink_attn_prefill(void* out, int64_t ldo, const float* q, const void* k
   if (dim <= 64 && vdim <= 64) return launch_prefill<4, 4, false>(SPF_ARGS);
   return launch_prefill<8, 8, false>(SPF_ARGS);
 #undef SPF_ARGS
+}
+
+int b200_sink_attn_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                             const float* r1, const float* r2, const float* sink, const int32_t* q_cu_lens,
+                             const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
+                             const int32_t* token_seq, int64_t rows, int64_t H, int64_t G, int64_t dim, int64_t vdim,
+                             int64_t block_size, float scale, int64_t n_splits, float* workspace,
+                             int64_t workspace_floats, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens && token_seq,
+                 "sink_attn_decode_tc: null pointer");
+  B200_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "sink_attn_decode_tc: the distance bias takes both of its numbers");
+  B200_CHECK_ARG(b200_sink_attn_prefill_supported(dim, vdim, dtype),
+                 "sink_attn_decode_tc: bf16 with head sizes that are multiples of 16 and at most 128");
+  B200_CHECK_ARG(rows > 0 && H > 0 && G > 0 && G <= 65535 && H % G == 0 && block_size > 0 && ldo >= H * vdim &&
+                     n_splits >= 1 && rows * n_splits < (1ll << 31) && is_aligned(k_cache, 16) && is_aligned(v_cache, 16),
+                 "sink_attn_decode_tc: bad shape or alignment");
+  B200_CHECK_ARG(n_splits == 1 || (workspace && workspace_floats >= rows * H * n_splits * (2 + vdim)),
+                 "sink_attn_decode_tc: workspace of rows * H * n_splits * (2 + vdim) floats required");
+  auto st = static_cast<cudaStream_t>(stream);
+#define SDT_ARGS out, ldo, q, k_cache, v_cache, r1, r2, sink, q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, \
+                 token_seq, rows, (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale, (int)n_splits, workspace, st
+  if (dim <= 64 && vdim <= 64) return launch_decode_tc<4, 4>(SDT_ARGS);
+  return launch_decode_tc<8, 8>(SDT_ARGS);
+#undef SDT_ARGS
 }
 
 }  // extern "C"

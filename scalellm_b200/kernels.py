@@ -1234,16 +1234,20 @@ def sink_attn_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor
 
 # a step whose longest portion has at least this many tokens runs the tensor-core kernel (bf16, fitting head sizes)
 SINK_ATTN_PREFILL_MIN_ROWS = 4
+# single tokens in bf16 with at least this many query heads per key/value head run as tensor-core tiles of heads
+SINK_ATTN_DECODE_TC_MIN_GROUP = 2
 
 
 def sink_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, r1: Optional[torch.Tensor],
               r2: Optional[torch.Tensor], sink: Optional[torch.Tensor], q_cu: torch.Tensor, kv_cu: torch.Tensor,
               block_tables: torch.Tensor, cu_block_lens: torch.Tensor, token_seq: torch.Tensor, block_size: int,
-              scale: float, n_seq: int = 0, q_max: int = 0, kv_max: int = 0) -> torch.Tensor:
+              scale: float, n_seq: int = 0, q_max: int = 0, kv_max: int = 0, n_splits: int = 0) -> torch.Tensor:
     """[rows, H * vdim] in the cache's dtype: causal softmax attention with the score scale q . k - r1 ln(1 + r2
     (i - j)) and exp(sink) added to the denominator (r1 / r2 / sink fp32 [H] or None).  With n_seq and q_max (the
     step's sequence count and longest portion, host numbers) a step with prompt portions in bf16 runs on the tensor
-    cores where the head sizes allow it; fp32 and odd sizes run the CUDA-core kernel."""
+    cores where the head sizes allow it; single tokens in bf16 with grouped heads run as tensor-core tiles of heads,
+    their keys shared out over several CTAs per row when the step has few rows (kv_max: an upper bound of the cached
+    lengths, sizes the split; n_splits forces it); fp32 and odd sizes run the CUDA-core kernel."""
     _cuda(q, k_cache, v_cache, r1, r2, sink)
     _f32(q, r1, r2, sink)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
@@ -1251,12 +1255,27 @@ def sink_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, r1:
     G, vdim = v_cache.shape[1], v_cache.shape[2]
     out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
     lib = _lib.load()
-    impl = os.environ.get("B200_SINK_ATTN_IMPL")      # "simt": CUDA cores throughout
+    impl = os.environ.get("B200_SINK_ATTN_IMPL")      # "simt": CUDA cores throughout; "simt_decode": for single tokens
     if (n_seq > 0 and q_max >= SINK_ATTN_PREFILL_MIN_ROWS and impl != "simt"
             and lib.b200_sink_attn_prefill_supported(dim, vdim, _dt(k_cache))):
         check(lib.b200_sink_attn_prefill(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(r1), _p(r2), _p(sink),
                                          _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens), n_seq, q_max, H, G,
                                          dim, vdim, block_size, scale, _dt(k_cache), _stream()))
+        return out
+    if (impl not in ("simt", "simt_decode") and H // G >= SINK_ATTN_DECODE_TC_MIN_GROUP
+            and lib.b200_sink_attn_prefill_supported(dim, vdim, _dt(k_cache))):
+        if n_splits <= 0:       # only steps with fewer CTAs than SMs are split, to about two CTAs per SM, two 64-key
+            # tiles each at least
+            tiles = max(1, -(-kv_max // 64))
+            ctas = rows * G * -(-(H // G) // 16)
+            n_splits = max(1, min(296 // ctas, tiles // 2, 64))
+        ws = None
+        if n_splits > 1:
+            ws = torch.empty(rows * H * n_splits * (2 + vdim), dtype=torch.float32, device=q.device)
+        check(lib.b200_sink_attn_decode_tc(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(r1), _p(r2), _p(sink),
+                                           _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens), _p(token_seq),
+                                           rows, H, G, dim, vdim, block_size, scale, n_splits, _p(ws),
+                                           ws.numel() if ws is not None else 0, _dt(k_cache), _stream()))
         return out
     check(lib.b200_sink_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(r1), _p(r2), _p(sink), _p(q_cu),
                              _p(kv_cu), _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,

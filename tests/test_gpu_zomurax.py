@@ -195,7 +195,8 @@ def test_attention_inputs_unit_length_temperature_and_value_blend(dtype, H, G, d
     assert float((q.cpu().double() - want_q).abs().max()) < 1e-5 * float(want_q.abs().max())
 
 
-def _attend_case(dtype, H, G, dim, vdim, block_size, cached, n_new, loud, bias=True, sink=True, seed=0, gain=6.0):
+def _attend_case(dtype, H, G, dim, vdim, block_size, cached, n_new, loud, bias=True, sink=True, seed=0, gain=6.0,
+                 n_splits=0):
     """The attention kernel alone over a hand-made cache: the query of row i points along key `loud[i]` with a length
     that lets this key take most of the row's weight.  Returns (got, want)."""
     from scalellm_b200 import kernels
@@ -223,11 +224,11 @@ def _attend_case(dtype, H, G, dim, vdim, block_size, cached, n_new, loud, bias=T
     dv = lambda t: None if t is None else t.to(DEV)
     got = kernels.sink_attn(q.to(DEV), kc.to(DEV), vc.to(DEV), dv(r1), dv(r2), dv(sk), par.q_cu_seq_lens,
                             par.kv_cu_seq_lens, par.block_tables, par.cu_block_lens, par.token_seq, block_size, scale,
-                            1, n_new, n)          # prompt-sized bf16 cases take the tensor-core kernel
+                            1, n_new, n, n_splits)   # bf16 cases of fitting sizes take the tensor-core kernels
     f64 = lambda t: None if t is None else t.double()
     # the tensor-core kernel rounds the queries to bf16 as the keys are
-    tensor_core = (dtype == torch.bfloat16 and n_new >= kernels.SINK_ATTN_PREFILL_MIN_ROWS and dim % 16 == 0
-                   and vdim % 16 == 0 and dim <= 128 and vdim <= 128)
+    tensor_core = (dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and dim <= 128 and vdim <= 128
+                   and (n_new >= kernels.SINK_ATTN_PREFILL_MIN_ROWS or H // G >= kernels.SINK_ATTN_DECODE_TC_MIN_GROUP))
     qr = q.to(torch.bfloat16).double() if tensor_core else q.double()
     want = oz.sink_attend(qr, K.double(), V.double(), pos, scale, f64(r1), f64(r2), f64(sk))
     return got.float().cpu().reshape(n_new, H, vdim).double(), want
@@ -243,8 +244,13 @@ def test_attention_far_keys_bias_and_sink(dtype, H, G, dim, vdim):
     tol = 1e-4 if dtype == torch.float32 else 0.05
     # one decoded token over 300 cached: key 1 decides although it is far; then prompt rows whose key is far back
     for bias, sink in ((True, True), (False, True), (True, False), (False, False)):
-        got, want = _attend_case(dtype, H, G, dim, vdim, 8, 300, 1, [1], bias, sink, seed=7, gain=9.0)
-        assert float((got - want).abs().max()) < tol, (bias, sink)
+        for n_splits in (0, 1, 2, 3, 9):      # the row's key tiles shared out over several CTAs, some left empty
+            got, want = _attend_case(dtype, H, G, dim, vdim, 8, 300, 1, [1], bias, sink, seed=7, gain=9.0, n_splits=n_splits)
+            assert float((got - want).abs().max()) < tol, (bias, sink, n_splits)
+    # three single tokens' worth of rows among many keys that all matter (no loud key), split and not
+    for n_splits in (0, 1, 4):
+        got, want = _attend_case(dtype, H, G, dim, vdim, 16, 700, 3, [None] * 3, seed=11, n_splits=n_splits)
+        assert float((got - want).abs().max()) < tol, n_splits
     got, want = _attend_case(dtype, H, G, dim, vdim, 16, 150, 70, [3 * i for i in range(70)], seed=dim, gain=9.0)
     assert float((got - want).abs().max()) < tol
     # the sink really takes weight: with it the rows are shorter than without
