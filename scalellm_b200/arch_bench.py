@@ -1,5 +1,6 @@
-"""Prefill and decode throughput of the Kigalix and Pokadra designs beside the Llama decoder at equal size
-(`bench.py --arch kigalix|pokadra`), all through the serving engine, random weights, bf16.
+"""Prefill and decode throughput of the Kigalix, Pokadra and Zomurax designs beside the Llama decoder (Zomurax also
+beside Kigalix, the design nearest to it) at equal size (`bench.py --arch kigalix|pokadra|zomurax`), all through the
+serving engine, random weights, bf16.
 
 Per size: tokens/s of a prompt step (B sequences of L tokens in one batch) and of decode steps (B sequences
 with L cached tokens, one token each), timed with CUDA events after warm-up; and, per kind of kernel, the
@@ -435,5 +436,171 @@ def run_pokadra(args) -> None:
         out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "pokadra": k, "llama": l,
                               "kernel_rooflines": pokadra_rooflines(s, batch, seqlen, k, l, peaks),
                               "attention_kernels": pokadra_attention_kernels(s, peaks),
+                              "seconds": round(time.time() - t0, 1)}
+    print(json.dumps(out))
+
+
+# ---------------------------------------------------------------------------
+# Zomurax beside Kigalix (latent attention, experts) and Llama (grouped-head attention, dense products)
+# ---------------------------------------------------------------------------
+ZOMURAX_EXTRA = {"w2048": dict(kv_heads=4, window=512, shared=1408, temp_every=1024),
+                 "w4096": dict(kv_heads=8, window=512, shared=2752, temp_every=1024)}
+ZOMURAX_KERNELS = ["bigram_embed", "sumnorm_residual", "group_rms_norm", "softcap_", "gated_act", "heads_to_rows",
+                   "latent_prepare", "latent_attn", "sink_attn_prepare", "sink_attn", "moe_table_route", "moe_plan",
+                   "grouped_gemm", "moe_combine"]
+
+
+def zomurax_config(s: dict) -> dict:
+    """Layers in the order latent, latent, attention, attention (the attention layers share values)."""
+    lat = {"type": "latent_attention", "mixer": {
+        "heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot"], "vdim": s["vdim"], "kv_rank": s["rank"],
+        "rot": {"base": 10000.0, "dims": s["rot"]}, "mask": {"size": s["window"]}, "scale": (s["dim"] + s["rot"]) ** -0.5}}
+    att = {"type": "attention", "mixer": {
+        "heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
+        "q_temp": {"coef": 0.1, "every": s["temp_every"]}, "v_mix": True}}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["shared"]}}
+    pattern = [lat, lat, att, att]
+    return {"architecture": "Zomurax", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5},
+            "postln_alpha": 2.0, "logit_softcap": 30.0,
+            "layers": [dict(pattern[i % 4], mlp=moe) for i in range(s["layers"])]}
+
+
+def zomurax_rooflines(s: dict, batch: int, seqlen: int, z: dict, k: dict, l: dict, peaks: dict) -> dict:
+    """Achieved fraction of the nearer roof per kind of kernel, from the per-kernel times of one step of each model
+    (all layers of that kind together), each beside the like kernel of the nearest existing model."""
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    n_lat = sum(1 for i in range(s["layers"]) if i % 4 < 2)
+    n_att = s["layers"] - n_lat
+    k_lat = sum(1 for i in range(s["layers"]) if i % 4 != 1)
+    k_moe = sum(1 for i in range(s["layers"]) if i % 4 != 0)
+    H, G, dim, vd, W, Dk = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["width"], s["rank"] + s["rot"]
+    out = {}
+    for phase in ("decode", "prefill"):
+        q_len = 1 if phase == "decode" else seqlen
+        ctx = seqlen + 1 if phase == "decode" else seqlen
+        rows = batch * q_len
+        zm, km, lm = z[phase]["kernels_ms"], k[phase]["kernels_ms"], l[phase]["kernels_ms"]
+        pairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        wpairs = batch * _visible_pairs(ctx, q_len, s["window"], 0)
+        touched = batch * (min(ctx, s["window"]) if phase == "decode" else ctx)
+        out[f"zomurax sink_attn {phase}"] = _frac(
+            zm.get("sink_attn", 0.0), n_att * (batch * ctx * G * (dim + vd) * 2 + rows * H * (dim * 4 + vd * 2)),
+            n_att * pairs * H * 2 * (dim + vd), hbm, tf)
+        Hl, Hkv = W // 128, max(1, W // 512)
+        out[f"llama paged attention {phase}"] = _frac(
+            lm.get("paged_kv_varlen_mha", 0.0), s["layers"] * (batch * ctx * 2 * Hkv * 128 * 2 + rows * Hl * 128 * 4),
+            s["layers"] * pairs * Hl * 4 * 128, hbm, tf)
+        out[f"zomurax latent_attn (window {s['window']}) {phase}"] = _frac(
+            zm.get("latent_attn", 0.0), n_lat * (touched * Dk * 2 + rows * H * (Dk + s["rank"]) * 4),
+            n_lat * wpairs * H * 2 * (Dk + s["rank"]), hbm, tf)
+        out[f"kigalix latent_attn {phase}"] = _frac(
+            km.get("latent_attn", 0.0), k_lat * (batch * ctx * Dk * 2 + rows * H * (Dk + s["rank"]) * 4),
+            k_lat * pairs * H * 2 * (Dk + s["rank"]), hbm, tf)
+        npairs = rows * s["top"]
+        ebytes = s["experts"] * 3 * s["eff"] * W * 2 + npairs * (W * 2 + 3 * s["eff"]) * 2
+        out[f"zomurax expert GEMMs {phase}"] = _frac(zm.get("grouped_gemm", 0.0), s["layers"] * ebytes,
+                                                    s["layers"] * npairs * 6 * s["eff"] * W, hbm, tf)
+        out[f"kigalix expert GEMMs {phase}"] = _frac(km.get("grouped_gemm", 0.0), k_moe * ebytes,
+                                                    k_moe * npairs * 6 * s["eff"] * W, hbm, tf)
+        # norm after the sum: reads x (4) and y (2), writes x (4) and its 16-bit copy (2) per channel, twice a layer
+        out[f"zomurax sumnorm_residual {phase}"] = _frac(zm.get("sumnorm_residual", 0.0), rows * W * 2 * s["layers"] * 12,
+                                                        0, hbm, tf)
+        out[f"llama rms_norm_residual {phase}"] = _frac(
+            lm.get("rms_norm_residual", 0.0) + lm.get("rms_norm", 0.0) + lm.get("rms_norm_residual_splitk", 0.0),
+            rows * W * (2 * s["layers"] + 1) * 4 * 2, 0, hbm, tf)
+        out[f"zomurax sink_attn_prepare {phase}"] = _frac(
+            zm.get("sink_attn_prepare", 0.0), n_att * rows * ((H + G) * dim * 2 + G * vd * 4 + H * dim * 4 + G * (dim + vd) * 2),
+            0, hbm, tf)
+        out[f"zomurax latent_prepare {phase}"] = _frac(
+            zm.get("latent_prepare", 0.0), n_lat * rows * (H * s["rot"] * 4 + 2 * Dk * 2), 0, hbm, tf)
+        out[f"kigalix latent_prepare {phase}"] = _frac(
+            km.get("latent_prepare", 0.0), k_lat * rows * (H * s["rot"] * 4 + 2 * Dk * 2), 0, hbm, tf)
+    return out
+
+
+def zomurax_attention_kernels(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 2048))) -> dict:
+    """The two attention kernels of the design alone beside their like kernels (Llama's paged attention with the same
+    heads; latent attention without a window), on caches larger than L2: (batch, cached length, new tokens per
+    sequence) = decoding over long contexts and one prompt portion.  CUDA events around 10 launches after 3."""
+    from . import kernels
+    from .decode_step import BlockPool, StepBuffers, build_step_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    H, G, dim, vd, rd, rank, win = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["rot"], s["rank"], s["window"]
+    bs, out = 16, {}
+    for batch, ctx, q_len in cases:
+        n_blocks = batch * (-(-ctx // bs)) + 8
+        pool = BlockPool(n_blocks, bs, seed=1)
+        seqs = []
+        for _ in range(batch):
+            sq = pool.open_sequence()
+            pool.reserve(sq, ctx)
+            seqs.append(sq)
+        hb = build_step_batch(pool, seqs, [[0] * q_len] * batch, [ctx - q_len] * batch, None)
+        tokens, positions, prm = StepBuffers(dev, batch * q_len, batch, n_blocks).upload(hb)
+        rows = batch * q_len
+        g = torch.Generator(device=dev).manual_seed(0)
+        rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        kc, vc = rnd(n_blocks * bs, G, dim), rnd(n_blocks * bs, G, vd)
+        q = torch.randn((rows, H, dim), generator=g, device=dev, dtype=torch.float32)
+        r1 = 0.1 + 0.3 * torch.rand(H, generator=g, device=dev)
+        r2 = 0.05 + 0.3 * torch.rand(H, generator=g, device=dev)
+        sk = torch.randn(H, generator=g, device=dev)
+        f_sink = lambda: kernels.sink_attn(q, kc, vc, r1, r2, sk, prm.q_cu_seq_lens, prm.kv_cu_seq_lens, prm.block_tables,
+                                           prm.cu_block_lens, prm.token_seq, bs, dim ** -0.5, batch, q_len, ctx)
+        f_plain = lambda: kernels.sink_attn(q, kc, vc, None, None, None, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                            prm.block_tables, prm.cu_block_lens, prm.token_seq, bs, dim ** -0.5, batch,
+                                            q_len, ctx)
+        kl, vl = rnd(n_blocks * bs, G, dim), rnd(n_blocks * bs, G, dim)
+        ql, ol = rnd(rows, H, dim), torch.empty((rows, H, dim), dtype=torch.bfloat16, device=dev)
+        f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kl, vl, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                      prm.block_tables, prm.cu_block_lens, None, bs, q_len, ctx,
+                                                      dim ** -0.5, 0.0, -1)
+        cache = rnd(n_blocks * bs, rank + rd)
+        qa, qq = rnd(H, rows, rank), rnd(rows, H * (dim + rd))
+        f_lat = lambda w: (lambda: kernels.latent_attn(qa, qq, cache, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                       prm.block_tables, prm.cu_block_lens, prm.token_seq, H, dim, rd,
+                                                       rank, bs, 0.07, ctx, w))
+        pairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        wpairs = batch * _visible_pairs(ctx, q_len, win, 0)
+        touched = batch * (min(ctx, win) if q_len == 1 else ctx)
+        a_bytes = batch * ctx * G * (dim + vd) * 2 + rows * H * (dim * 4 + vd * 2)
+        for name, fn, nbytes, flops in (
+                ("zomurax sink_attn", f_sink, a_bytes, pairs * H * 2 * (dim + vd)),
+                ("zomurax sink_attn without bias and sink", f_plain, a_bytes, pairs * H * 2 * (dim + vd)),
+                ("llama paged attention, same heads", f_llama, batch * ctx * 2 * G * dim * 2 + rows * H * dim * 4,
+                 pairs * H * 4 * dim),
+                (f"zomurax latent_attn, window {win}", f_lat(win), touched * (rank + rd) * 2 + rows * H * (2 * rank + rd) * 2,
+                 wpairs * H * 2 * (2 * rank + rd)),
+                ("kigalix latent_attn (no window)", f_lat(0), batch * ctx * (rank + rd) * 2 + rows * H * (2 * rank + rd) * 2,
+                 pairs * H * 2 * (2 * rank + rd))):
+            ms = _time_steps(fn, 3, 10)
+            out[f"{name}, {batch} x {ctx} cached, {q_len} new"] = _frac(ms, nbytes, flops, hbm, tf)
+        del kc, vc, kl, vl, cache
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_zomurax(args) -> None:
+    torch.cuda.set_device(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    out = {"metric": "zomurax_vs_kigalix_vs_llama_tokens_per_s", "unit": "tokens/s", "dtype": "bf16",
+           "data": "synthetic (random-init weights, random token ids)", "n_gpus": 1,
+           "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                     "source": "measured" if os.path.exists(peaks_path) else "fallback"}, "sizes": {}}
+    names = [args.arch_size] if args.arch_size != "all" else list(SIZES)
+    for name in names:
+        s = dict(SIZES[name], **ZOMURAX_EXTRA[name])
+        batch, seqlen = args.arch_batch, args.arch_seqlen
+        t0 = time.time()
+        z = _run_model(zomurax_config(s), batch, seqlen, args.warmup, args.steps, ZOMURAX_KERNELS)
+        k = _run_model(kigalix_config(s), batch, seqlen, args.warmup, args.steps, KIGALIX_KERNELS)
+        l = _run_model(llama_config(s), batch, seqlen, args.warmup, args.steps, LLAMA_KERNELS)
+        out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "zomurax": z, "kigalix": k, "llama": l,
+                              "kernel_rooflines": zomurax_rooflines(s, batch, seqlen, z, k, l, peaks),
+                              "attention_kernels": zomurax_attention_kernels(s, peaks),
                               "seconds": round(time.time() - t0, 1)}
     print(json.dumps(out))

@@ -267,7 +267,7 @@ __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint3
 // dim <= 16 KS_MAX, vdim <= 16 VT_MAX, both multiples of 16; EXACT: dim = 16 KS_MAX and vdim = 16 VT_MAX, known to
 // the compiler
 template <int KS_MAX, int VT_MAX, bool EXACT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, EXACT ? 4 : 1)
 sink_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                          const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink,
@@ -476,6 +476,8 @@ int launch_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, 
 // hands its merged sums to sink_attn_merge_kernel through a workspace; the sink joins the sum at the very end.
 // ------------------------------------------------------------------------------------------------------------
 constexpr int kDK = 64;
+constexpr int kDS = 2;      // staged tiles: one in flight while one is consumed (a third measured slower: the walk is
+                            // bound by its own latency, and shared memory bounds the CTAs per SM)
 
 template <int KS_MAX, int VT_MAX>
 __global__ void __launch_bounds__(128)
@@ -492,8 +494,8 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   float* ml_s = reinterpret_cast<float*>(Qs + 16 * KROW);          // [4 warps][2: m, l][16 rows]
   float* b_s = ml_s + 4 * 2 * 16;                                  // [2: r1, r2][16 rows]
   unsigned char* big = reinterpret_cast<unsigned char*>(b_s + 2 * 16);
-  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [2][kDK][KROW]
-  __nv_bfloat16* Vs = Ks + 2 * kDK * KROW;                         // [2][kDK][VROW]
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [kDS][kDK][KROW]
+  __nv_bfloat16* Vs = Ks + kDS * kDK * KROW;                       // [kDS][kDK][VROW]
   float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][16][vdim]
   const int row = blockIdx.x / n_splits, split = blockIdx.x % n_splits, g = blockIdx.y, warp = threadIdx.x >> 5,
             lane = threadIdx.x & 31;
@@ -521,24 +523,26 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   const int tile0 = split * per;
   const int n_tiles = all_tiles - tile0 < per ? (all_tiles - tile0 > 0 ? all_tiles - tile0 : 0) : per;
   const size_t k_stride = (size_t)G * dim, v_stride = (size_t)G * vdim;
-  auto load_tile = [&](int idx, int buf) {
-    const int j0 = (tile0 + idx) * kDK;
-    const int sub = threadIdx.x & 1;
-    for (int key = threadIdx.x >> 1; key < kDK; key += 64) {
-      const int j = j0 + key;
-      const bool ok = j <= i;
-      size_t slot = 0;
-      if (ok) slot = (size_t)table[j / block_size] + j % block_size;
-      const __nv_bfloat16* kr = k_cache + slot * k_stride + (size_t)g * dim;
-      const __nv_bfloat16* vr = v_cache + slot * v_stride + (size_t)g * vdim;
-      __nv_bfloat16* kd = Ks + ((size_t)buf * kDK + key) * KROW;
-      __nv_bfloat16* vd = Vs + ((size_t)buf * kDK + key) * VROW;
-      for (int c = sub; c < dim / 8; c += 2) cp_async16(kd + c * 8, kr + c * 8, ok);
-      for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
-    }
+  // two threads per key of a tile; the key's cache row is looked up in the block table one tile ahead of its copy,
+  // so that the lookup's latency is off the walk's critical path
+  const int my_key = threadIdx.x >> 1, sub = threadIdx.x & 1;
+  auto slot_of = [&](int idx) -> long long {
+    const int j = (tile0 + idx) * kDK + my_key;
+    return (idx < n_tiles && j <= i) ? (long long)table[j / block_size] + j % block_size : -1;
   };
-  if (n_tiles > 0) load_tile(0, 0);
+  auto load_tile = [&](long long slot, int buf) {
+    const bool ok = slot >= 0;
+    const size_t sl = ok ? (size_t)slot : 0;
+    const __nv_bfloat16* kr = k_cache + sl * k_stride + (size_t)g * dim;
+    const __nv_bfloat16* vr = v_cache + sl * v_stride + (size_t)g * vdim;
+    __nv_bfloat16* kd = Ks + ((size_t)buf * kDK + my_key) * KROW;
+    __nv_bfloat16* vd = Vs + ((size_t)buf * kDK + my_key) * VROW;
+    for (int c = sub; c < dim / 8; c += 2) cp_async16(kd + c * 8, kr + c * 8, ok);
+    for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
+  };
+  if (n_tiles > 0) load_tile(slot_of(0), 0);
   cp_async_commit();
+  long long next_slot = slot_of(1);
   const int gr = lane >> 2, qc = (lane & 3) * 2;
   float mx[2] = {-INFINITY, -INFINITY}, ls[2] = {0.0f, 0.0f};
   float o[VT_MAX * 2][4];
@@ -549,8 +553,9 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
     const int buf = it & 1;
     cp_async_wait_all();                                   // tile `it` has landed
     __syncthreads();                                       // and everyone is done with tile it - 1 (and Qs, b_s stand)
-    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
+    if (it + 1 < n_tiles) load_tile(next_slot, buf ^ 1);
     cp_async_commit();
+    next_slot = slot_of(it + 2);
     if (it == 0) { hb1[0] = b_s[gr]; hb1[1] = b_s[gr + 8]; hb2[0] = b_s[16 + gr]; hb2[1] = b_s[16 + gr + 8]; }
     const int j0 = (tile0 + it) * kDK + warp * 16;       // this warp's 16 keys of the tile
     if (j0 > i) continue;                                // all after the row's position
@@ -719,7 +724,7 @@ int launch_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache
                      const int* blk_cu, const int* token_seq, int64_t rows, int H, int G, int dim, int vdim,
                      int block_size, float scale, int n_splits, float* ws, cudaStream_t st) {
   const int R = H / G;
-  const size_t tiles = ((size_t)2 * kDK * (dim + 8) + (size_t)2 * kDK * (vdim + 8)) * sizeof(__nv_bfloat16);
+  const size_t tiles = ((size_t)kDS * kDK * (dim + 8) + (size_t)kDS * kDK * (vdim + 8)) * sizeof(__nv_bfloat16);
   const size_t sums = (size_t)4 * 16 * vdim * sizeof(float);
   const size_t smem = (size_t)16 * (dim + 8) * sizeof(__nv_bfloat16) + (4 * 2 * 16 + 2 * 16) * sizeof(float) +
                       (tiles > sums ? tiles : sums);
