@@ -493,7 +493,8 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);     // [16][KROW]
   float* ml_s = reinterpret_cast<float*>(Qs + 16 * KROW);          // [4 warps][2: m, l][16 rows]
   float* b_s = ml_s + 4 * 2 * 16;                                  // [2: r1, r2][16 rows]
-  unsigned char* big = reinterpret_cast<unsigned char*>(b_s + 2 * 16);
+  int* slot_s = reinterpret_cast<int*>(b_s + 2 * 16);              // [2][kDK] cache rows of the keys of two tiles
+  unsigned char* big = reinterpret_cast<unsigned char*>(slot_s + 2 * kDK);
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(big);       // [kDS][kDK][KROW]
   __nv_bfloat16* Vs = Ks + kDS * kDK * KROW;                       // [kDS][kDK][VROW]
   float* o_s = reinterpret_cast<float*>(big);                      // after the walk: [4 warps][16][vdim]
@@ -523,26 +524,37 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
   const int tile0 = split * per;
   const int n_tiles = all_tiles - tile0 < per ? (all_tiles - tile0 > 0 ? all_tiles - tile0 : 0) : per;
   const size_t k_stride = (size_t)G * dim, v_stride = (size_t)G * vdim;
-  // two threads per key of a tile; the key's cache row is looked up in the block table one tile ahead of its copy,
-  // so that the lookup's latency is off the walk's critical path
-  const int my_key = threadIdx.x >> 1, sub = threadIdx.x & 1;
-  auto slot_of = [&](int idx) -> long long {
-    const int j = (tile0 + idx) * kDK + my_key;
-    return (idx < n_tiles && j <= i) ? (long long)table[j / block_size] + j % block_size : -1;
+  // The cache rows of a tile's keys are looked up in the block table one tile ahead of their copy (threads 0..63, one
+  // key each, into slot_s), so that the lookup's latency is off the walk's critical path; the copy itself runs with
+  // consecutive lanes on consecutive 16-byte pieces of a row, a few full lines per instruction.
+  auto lookup = [&](int idx) {
+    if (threadIdx.x < kDK) {
+      const int j = (tile0 + idx) * kDK + threadIdx.x;
+      slot_s[(idx & 1) * kDK + threadIdx.x] =
+          (idx < n_tiles && j <= i) ? table[j / block_size] + j % block_size : -1;
+    }
   };
-  auto load_tile = [&](long long slot, int buf) {
-    const bool ok = slot >= 0;
-    const size_t sl = ok ? (size_t)slot : 0;
-    const __nv_bfloat16* kr = k_cache + sl * k_stride + (size_t)g * dim;
-    const __nv_bfloat16* vr = v_cache + sl * v_stride + (size_t)g * vdim;
-    __nv_bfloat16* kd = Ks + ((size_t)buf * kDK + my_key) * KROW;
-    __nv_bfloat16* vd = Vs + ((size_t)buf * kDK + my_key) * VROW;
-    for (int c = sub; c < dim / 8; c += 2) cp_async16(kd + c * 8, kr + c * 8, ok);
-    for (int c = sub; c < vdim / 8; c += 2) cp_async16(vd + c * 8, vr + c * 8, ok);
+  const int CK = dim / 8, CV = vdim / 8;                 // 16-byte pieces per key row and value row
+  auto load_tile = [&](int idx, int buf) {
+    const int* sl = slot_s + (idx & 1) * kDK;
+    for (int id = threadIdx.x; id < kDK * CK; id += 128) {
+      const int key = id / CK, c = id - key * CK;
+      const int slot = sl[key];
+      cp_async16(Ks + ((size_t)buf * kDK + key) * KROW + c * 8,
+                 k_cache + (size_t)(slot < 0 ? 0 : slot) * k_stride + (size_t)g * dim + c * 8, slot >= 0);
+    }
+    for (int id = threadIdx.x; id < kDK * CV; id += 128) {
+      const int key = id / CV, c = id - key * CV;
+      const int slot = sl[key];
+      cp_async16(Vs + ((size_t)buf * kDK + key) * VROW + c * 8,
+                 v_cache + (size_t)(slot < 0 ? 0 : slot) * v_stride + (size_t)g * vdim + c * 8, slot >= 0);
+    }
   };
-  if (n_tiles > 0) load_tile(slot_of(0), 0);
+  lookup(0);
+  lookup(1);
+  __syncthreads();
+  if (n_tiles > 0) load_tile(0, 0);
   cp_async_commit();
-  long long next_slot = slot_of(1);
   const int gr = lane >> 2, qc = (lane & 3) * 2;
   float mx[2] = {-INFINITY, -INFINITY}, ls[2] = {0.0f, 0.0f};
   float o[VT_MAX * 2][4];
@@ -553,9 +565,9 @@ sink_attn_decode_tc_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const f
     const int buf = it & 1;
     cp_async_wait_all();                                   // tile `it` has landed
     __syncthreads();                                       // and everyone is done with tile it - 1 (and Qs, b_s stand)
-    if (it + 1 < n_tiles) load_tile(next_slot, buf ^ 1);
+    if (it + 1 < n_tiles) load_tile(it + 1, buf ^ 1);
     cp_async_commit();
-    next_slot = slot_of(it + 2);
+    lookup(it + 2);                                        // into the half of slot_s that tile `it` has left
     if (it == 0) { hb1[0] = b_s[gr]; hb1[1] = b_s[gr + 8]; hb2[0] = b_s[16 + gr]; hb2[1] = b_s[16 + gr + 8]; }
     const int j0 = (tile0 + it) * kDK + warp * 16;       // this warp's 16 keys of the tile
     if (j0 > i) continue;                                // all after the row's position
@@ -727,7 +739,7 @@ int launch_decode_tc(void* out, int64_t ldo, const float* q, const void* k_cache
   const size_t tiles = ((size_t)kDS * kDK * (dim + 8) + (size_t)kDS * kDK * (vdim + 8)) * sizeof(__nv_bfloat16);
   const size_t sums = (size_t)4 * 16 * vdim * sizeof(float);
   const size_t smem = (size_t)16 * (dim + 8) * sizeof(__nv_bfloat16) + (4 * 2 * 16 + 2 * 16) * sizeof(float) +
-                      (tiles > sums ? tiles : sums);
+                      2 * kDK * sizeof(int) + (tiles > sums ? tiles : sums);
   auto kern = sink_attn_decode_tc_kernel<KS_MAX, VT_MAX>;
   if (smem > 48 * 1024)
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

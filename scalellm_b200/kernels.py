@@ -1264,11 +1264,13 @@ def sink_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, r1:
         return out
     if (impl not in ("simt", "simt_decode") and H // G >= SINK_ATTN_DECODE_TC_MIN_GROUP
             and lib.b200_sink_attn_prefill_supported(dim, vdim, _dt(k_cache))):
-        if n_splits <= 0:       # only steps with fewer CTAs than SMs are split, to about two CTAs per SM, two 64-key
-            # tiles each at least
+        if n_splits <= 0:
+            # steps with fewer CTAs than SMs are split to about two CTAs per SM; walks of 32 tiles (2 048 keys) and
+            # more are cut in four whatever the step's size (measured: a CTA's walk is bound by its own latency, and
+            # four shorter walks per row keep three CTAs resident per SM); never fewer than two 64-key tiles a share
             tiles = max(1, -(-kv_max // 64))
             ctas = rows * G * -(-(H // G) // 16)
-            n_splits = max(1, min(296 // ctas, tiles // 2, 64))
+            n_splits = max(1, min(max(296 // ctas, 4 if tiles >= 32 else 1), tiles // 2, 64))
         ws = None
         if n_splits > 1:
             ws = torch.empty(rows * H * n_splits * (2 + vdim), dtype=torch.float32, device=q.device)
