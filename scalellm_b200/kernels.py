@@ -590,6 +590,10 @@ def silu_mul_splitk(partials: W4Partials, dtype: torch.dtype = torch.bfloat16) -
     return out
 
 
+def silu_mul_splitk_available() -> bool:
+    return _lib.has("b200_silu_mul_splitk")
+
+
 def rms_norm_residual_splitk(out: torch.Tensor, residual: torch.Tensor, partials: W4Partials,
                              weight: torch.Tensor, epsilon: float) -> None:
     """residual += T(sum over slots of partials); out = rms_norm(residual) * weight."""

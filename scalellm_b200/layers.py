@@ -692,9 +692,10 @@ class LatentAttention:
 
     def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, dim: int, rot_dim: int, vdim: int, rank: int,
                  scale: float, inv_freq: torch.Tensor, rot_mult: float, rot_dims: int, eps: float,
-                 dtype: torch.dtype, device, window: int = 0, half_pairs: bool = False):
+                 dtype: torch.dtype, device, window: int = 0, half_pairs: bool = False, fusable_out: bool = False):
+        """fusable_out: hand on the output projection's split-K partials where a fused consumer can take them."""
         self.H, self.dim, self.rd, self.vd, self.rank = n_heads, dim, rot_dim, vdim, rank
-        self.window, self.half_pairs = window, half_pairs
+        self.window, self.half_pairs, self.fusable_out = window, half_pairs, fusable_out
         self.scale, self.rot_mult, self.rot_dims, self.eps, self.dtype = scale, rot_mult, rot_dims, eps, dtype
         self.inv_freq = inv_freq.to(torch.float32).to(device).contiguous()
         qw = n_heads * (dim + rot_dim)
@@ -722,7 +723,7 @@ class LatentAttention:
                                   cache.block_size(), self.scale, params.kv_max_seq_len, self.window)
         o = torch.bmm(lat, self.uv_t)                                           # [H, T, vdim]
         o = kernels.heads_to_rows(o, proj[:, self.dkv_end:] if self.has_gate else None)
-        return self.o_proj(o)
+        return self.o_proj.forward_fusable(o) if self.fusable_out else self.o_proj(o)
 
     __call__ = forward
 
@@ -758,12 +759,17 @@ class DeltaRuleMixer:
 
 
 class GatedMLP:
-    """down(act(gate h) * (up h)); act "silu" or "gelu_tanh".  gate and up share one GEMM."""
+    """down(act(gate h) * (up h)); act "silu" or "gelu_tanh".  gate and up share one GEMM.  For decode-sized bf16
+    steps the SiLU form takes the split-K partials of that GEMM (its reduction folded into the activation launch)."""
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, act: str):
         self.gate_up, self.down, self.act = Linear(torch.cat([gate, up], dim=0)), Linear(down), act
+        self.ff = gate.shape[0]
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
+        if (self.act == "silu" and h.dtype == torch.bfloat16 and self.ff % 64 == 0
+                and self.gate_up.supports_partials(h.shape[0]) and kernels.silu_mul_splitk_available()):
+            return self.down(kernels.silu_mul_splitk(self.gate_up.forward_partials(h), h.dtype))
         return self.down(kernels.gated_act(self.gate_up(h), self.act))
 
     __call__ = forward

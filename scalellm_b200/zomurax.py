@@ -179,7 +179,7 @@ class ZomuraxDecoder:
                 lay.mixer = LatentAttention(mw, int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]),
                                             int(m["kv_rank"]), float(m["scale"]), rotary_table(rot), 1.0,
                                             int(rot["dims"]), eps, dt, dev, window=int(mask.get("size", 0)),
-                                            half_pairs=True)
+                                            half_pairs=True, fusable_out=True)
             else:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
             lay.norm1 = SumNormResidual(f32(p + "norm1"), self.alpha, eps)
