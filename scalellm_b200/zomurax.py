@@ -52,7 +52,8 @@ def tensor_shapes(config: dict) -> Dict[str, tuple]:
         p, m = f"l{i}.", L["mixer"]
         out[p + "norm1"] = ()
         if L["type"] == "attention":
-            H, G, dim, vd = (int(m[k]) for k in ("heads", "kv_heads", "dim", "vdim"))
+            H, dim = int(m["heads"]), int(m["dim"])
+            G, vd = int(m.get("kv_heads", H)), int(m.get("vdim", dim))
             out.update({p + "mix.q": (H * dim, W), p + "mix.k": (G * dim, W), p + "mix.v": (G * vd, W),
                         p + "mix.o": (W, H * vd), p + "mix.r1": (H,), p + "mix.r2": (H,), p + "mix.sink": (H,)})
             if m.get("v_mix"):
@@ -146,7 +147,7 @@ class ZomuraxDecoder:
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         dev, dt, eps, W = self.device, self.dtype, self.eps, self.width
-        optional = (".r1", ".r2", ".sink")
+        optional = (".r1", ".r2", ".sink", ".vmix")      # (the first value-sharing layer has no use for its ".vmix")
         missing = [n for n in tensor_shapes(self.config) if n not in tensors and not n.endswith(optional)]
         if missing:
             raise KeyError(f"checkpoint lacks {missing[:5]}{' ...' if len(missing) > 5 else ''}")
@@ -170,7 +171,8 @@ class ZomuraxDecoder:
                 if lay.shares_values and sharing_seen:      # the first sharing layer gives, the later ones blend
                     lam = float(tensors[p + "mix.vmix"].float())
                 sharing_seen = sharing_seen or lay.shares_values
-                lay.mixer = SinkAttention(mw, int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]),
+                lay.mixer = SinkAttention(mw, int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]),
+                                          int(m.get("vdim", m["dim"])),
                                           float(m["scale"]), float(qt.get("coef", 0.0)), int(qt.get("every", 0)), lam,
                                           eps, dt, dev)
             elif L["type"] == "latent_attention":
@@ -178,7 +180,7 @@ class ZomuraxDecoder:
                 mask = m.get("mask") or {}
                 lay.mixer = LatentAttention(mw, int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]),
                                             int(m["kv_rank"]), float(m["scale"]), rotary_table(rot), 1.0,
-                                            int(rot["dims"]), eps, dt, dev, window=int(mask.get("size", 0)),
+                                            int(rot["dims"]), eps, dt, dev, window=int(mask.get("size") or 0),
                                             half_pairs=True, fusable_out=True)
             else:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
@@ -205,8 +207,8 @@ class ZomuraxDecoder:
         for lay, L in zip(self.layers, self.config["layers"]):
             m = L["mixer"]
             if L["type"] == "attention":
-                lay.cache = KVCache(n_blocks, block_size, int(m["kv_heads"]), int(m["dim"]), self.dtype, self.device,
-                                    value_dim=int(m["vdim"]))
+                lay.cache = KVCache(n_blocks, block_size, int(m.get("kv_heads", m["heads"])), int(m["dim"]), self.dtype,
+                                    self.device, value_dim=int(m.get("vdim", m["dim"])))
             else:
                 lay.cache = LatentKVCache(n_blocks, block_size, int(m["kv_rank"]), int(m["rot_dim"]), self.dtype,
                                           self.device)
