@@ -729,6 +729,82 @@ B200_API int b200_sink_attn_decode_tc(void* out, int64_t ldo, const float* q, co
                                       int64_t n_splits, float* workspace /*nullable*/, int64_t workspace_floats,
                                       int dtype, b200_stream_t stream);
 
+/* ---- sigmoid attention inside blocks of positions with a head mix, gated delta rule with short input filters,
+ * softmax router with group limits and pass-through outputs, branch norms (sigmoid_attn.cu, delta_rule.cu, moe.cu,
+ * postnorm.cu).  The reference has no such operators; each entry states its arithmetic. ---- */
+/* Per token: q_out[row, h] = turn(q_in[row, h] + q_bias) as fp32; k_cache[slot, g] = turn(k_in[row, g] + k_bias);
+ * v_cache[slot] = v_in[row] + v_bias.  turn: the first rot_dims channels of a head, channel t with t + rot_dims / 2,
+ * by the angle position * inv_freq[t] (fp32).  q_in / k_in / v_in: column blocks of one matrix (row stride ld);
+ * biases fp32, nullable. */
+B200_API int b200_sigmoid_attn_prepare(float* q_out, const void* q_in, const void* k_in, const void* v_in, int64_t ld,
+                                       const float* q_bias /*nullable*/, const float* k_bias /*nullable*/,
+                                       const float* v_bias /*nullable*/, void* k_cache, void* v_cache,
+                                       const float* inv_freq /*nullable when rot_dims == 0*/,
+                                       const int32_t* positions, const int32_t* slots, int64_t rows, int64_t H,
+                                       int64_t G, int64_t dim, int64_t vdim, int64_t rot_dims, int dtype,
+                                       b200_stream_t stream);
+/* out[row, h] = sum_j a'_hj v_j over the cached rows j <= position i of the row with floor(j / size) = floor(i / size)
+ * (size 0: all j <= i); a_hj = sigmoid(cap tanh(scale q_h . k_j / cap) + head_bias[h]) (cap 0: no cap), not normalised;
+ * a'_hj = sum_g head_mix[h, g] a_gj (head_mix fp32 [H, H], nullable: a' = a).  q fp32 [rows, H, dim]; caches
+ * [slots, G, dim] and [slots, G, vdim] of type `dtype`.  rows_per_cta: a hint (the longest portion of the step): CTAs
+ * take up to 8 consecutive rows and share the key tiles among them.  CUDA cores, any sizes with H * vdim <= 8192. */
+B200_API int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                               const float* head_bias /*nullable*/, const float* head_mix /*nullable*/,
+                               const int32_t* q_cu_lens, const int32_t* kv_cu_lens, const int32_t* block_tables,
+                               const int32_t* cu_block_lens, const int32_t* token_seq, int64_t rows, int64_t H,
+                               int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale, float cap,
+                               int64_t size, int64_t rows_per_cta, int dtype, b200_stream_t stream);
+/* Inputs of the gated delta rule for every row: x = silu(filter(x_in)) with causal per-channel filters [channels, taps]
+ * (last column: the current token; lags before the step come from filter_state [n_slots, taps - 1, 2 G dim + H vdim],
+ * lags before position 0 are zero); q, k [rows, G, dim] made unit length per head (eps unit_eps under the root), q also
+ * times dim^(-1/2); v [rows, H, vdim]; decay[row, h, c] = exp(-exp(a_log[h]) softplus(decay_in + dt_bias));
+ * beta[row, h] = sigmoid(beta_in).  q_in, k_in, v_in, beta_in: column blocks of one matrix (row stride ld).  Then
+ * filter_state takes the last taps - 1 inputs of every sequence.  All outputs fp32. */
+B200_API int b200_gated_delta_prepare(float* q_out, float* k_out, float* v_out, float* decay_out, float* beta_out,
+                                      const void* q_in, const void* k_in, const void* v_in, const void* beta_in,
+                                      int64_t ld, const void* decay_in, int64_t ld_decay, const float* q_filter,
+                                      const float* k_filter, const float* v_filter, const float* a_log,
+                                      const float* dt_bias, float* filter_state, const int32_t* q_cu_lens,
+                                      const int32_t* positions, const int32_t* token_seq, const int32_t* state_slots,
+                                      int64_t rows, int64_t n_seq, int64_t H, int64_t G, int64_t dim, int64_t vdim,
+                                      int64_t taps, float unit_eps, int dtype, b200_stream_t stream);
+/* Per (sequence, head), over the sequence's rows in order, S [dim, vdim] fp32 in state[slot, h] (zero where the
+ * portion starts at position 0):  S <- diag(decay) S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q ;
+ * out[row, h] = o / rms(o) * norm_weight[vdim] * sigmoid(gate_logits[row, h]).  Head h reads q / k head h / (H / G).
+ * dim <= 128, vdim <= 256. */
+B200_API int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k, const float* v,
+                                   const float* decay, const float* beta, const void* gate_logits, int64_t ld_gate,
+                                   const float* norm_weight, float* state, const int32_t* q_cu_lens,
+                                   const int32_t* positions, const int32_t* state_slots, int64_t n_seq, int64_t H,
+                                   int64_t G, int64_t dim, int64_t vdim, float eps, int dtype, b200_stream_t stream);
+/* p = softmax(router_weight h) over E outputs (fp32); choice score c = p + correction (nullable); the outputs form
+ * n_groups equal runs of neighbours and only the keep_groups runs with the largest max c can be chosen; the `top`
+ * largest c are chosen; weights = chosen p / (their sum + weight_eps).  extra_weight (nullable, fp32 [W]):
+ * extra_out[row] = sigmoid(extra_weight . h). */
+B200_API int b200_moe_route_softmax(int32_t* expert_ids, float* weights, float* extra_out /*nullable*/, const void* h,
+                                    int64_t ldh, const float* router_weight, const float* correction /*nullable*/,
+                                    const float* extra_weight /*nullable*/, int64_t rows, int64_t W, int64_t E,
+                                    int64_t top, int64_t n_groups, int64_t keep_groups, float weight_eps, int dtype,
+                                    b200_stream_t stream);
+/* out[row] = sum_k pair_weights[row, k] * (expert_ids[row, k] < n_real ? Y[pos_of_pair[row, k]] : h[row])
+ * (+ addend_gate[row] * addend[row]; gate nullable: 1). */
+B200_API int b200_moe_combine_weighted(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair,
+                                       const int32_t* expert_ids, const float* pair_weights, int64_t n_real,
+                                       const void* h, int64_t ldh, int64_t rows, int64_t W, int64_t top,
+                                       const void* addend /*nullable*/, int64_t ld_add,
+                                       const float* addend_gate /*nullable*/, int dtype, b200_stream_t stream);
+/* m = 1/2 (a / rms(a) * weight_a + b / rms(b) * weight_b), or m = a / rms(a) * weight_a without b, or m = a without
+ * weight_a;  x_out = x_in + m / rms(m) * weight;  h_out (nullable) = x_out / rms(x_out) * weight_next as T, or x_out
+ * as T without weight_next.  x fp32 [rows, W]; a, b of type T with row strides lda, ldb. */
+B200_API int b200_branch_norm_residual(float* x_out, void* h_out /*nullable*/, const float* x_in, const void* a,
+                                       int64_t lda, const void* b /*nullable*/, int64_t ldb,
+                                       const float* weight_a /*nullable*/, const float* weight_b /*nullable*/,
+                                       const float* weight, const float* weight_next /*nullable*/, int64_t rows,
+                                       int64_t W, float eps, int dtype, b200_stream_t stream);
+/* out [rows, n] = max(in, 0)^2 for the first n columns of rows with stride ld_in. */
+B200_API int b200_relu_squared(void* out, const void* in, int64_t rows, int64_t n, int64_t ld_in, int dtype,
+                               b200_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

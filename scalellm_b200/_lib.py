@@ -160,6 +160,24 @@ SIGNATURES = {
                                         _i64, _i64, _i64, _i64, _f32, _i64, _vp, _i64, _int, _vp]),
     "b200_sink_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64,
                                       _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    # sigmoid attention in blocks of positions with a head mix, gated delta rule with input filters, softmax router
+    # with group limits, branch norms (sigmoid_attn.cu, delta_rule.cu, moe.cu, postnorm.cu)
+    "b200_sigmoid_attn_prepare": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                         _i64, _i64, _i64, _i64, _int, _vp]),
+    "b200_sigmoid_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
+                                 _i64, _i64, _f32, _f32, _i64, _i64, _int, _vp]),
+    "b200_gated_delta_prepare": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
+                                        _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
+                                        _f32, _int, _vp]),
+    "b200_gated_delta_scan": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
+                                     _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+    "b200_moe_route_softmax": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                      _f32, _int, _vp]),
+    "b200_moe_combine_weighted": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64,
+                                         _vp, _int, _vp]),
+    "b200_branch_norm_residual": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _f32,
+                                         _int, _vp]),
+    "b200_relu_squared": (_int, [_vp, _vp, _i64, _i64, _i64, _int, _vp]),
 }
 
 # Which source files a partial library needs for a group of entry points.  The whole library
@@ -167,7 +185,7 @@ SIGNATURES = {
 # just the sources a model asks for into a library of its own.
 ALL_SOURCES = ("runtime.cu", "elementwise.cu", "sampling.cu", "paged_attn.cu", "prefill_attn.cu", "w4a16.cu",
                "dense.cu", "allreduce.cu", "hyper.cu", "latent_attn.cu", "delta_rule.cu", "moe.cu", "postnorm.cu", "mingru.cu",
-               "diff_attn.cu", "sink_attn.cu")
+               "diff_attn.cu", "sink_attn.cu", "sigmoid_attn.cu")
 
 _lib: Optional[C.CDLL] = None
 _lib_sources: frozenset = frozenset()

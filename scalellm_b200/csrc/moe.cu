@@ -273,6 +273,117 @@ __global__ void moe_table_route_kernel(int* __restrict__ ids, const int* __restr
   }
 }
 
+// Softmax router with a choice correction and a limit to the best groups:
+//     p = softmax(Wr h) over the E outputs (fp32) ;  c = p + correction
+//     the E outputs form n_groups equal runs of neighbours; a run's score is its largest c; outside the keep_groups
+//     best runs c counts as -inf
+//     the `top` largest c are chosen (first index wins a tie); weight = p / (sum of the chosen p + weight_eps)
+// extra_w (nullable): one more row for the same input, extra_out[row] = sigmoid(extra_w . h) (a gate every token gets).
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_softmax_kernel(int* __restrict__ ids, float* __restrict__ weights, float* __restrict__ extra_out,
+                         const T* __restrict__ h, int64_t ldh, const float* __restrict__ Wr,
+                         const float* __restrict__ correction, const float* __restrict__ extra_w, int W, int E,
+                         int top, int n_groups, int keep_groups, float weight_eps) {
+  __shared__ float z_s[kMaxExperts + 1];     // logits, then probabilities
+  __shared__ float c_s[kMaxExperts];         // choice scores
+  __shared__ unsigned char dead[kMaxExperts];
+  __shared__ float red[32];
+  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* x = h + (size_t)row * ldh;
+  const int n_dots = E + (extra_w ? 1 : 0);
+  for (int e = warp; e < n_dots; e += 4) {
+    const float* w = e < E ? Wr + (size_t)e * W : extra_w;
+    float acc = 0.0f;
+    for (int i = lane; i < W; i += 32) acc += Num<T>::to_f(x[i]) * w[i];
+    acc = warp_sum(acc);
+    if (lane == 0) z_s[e] = acc;
+  }
+  __syncthreads();
+  if (extra_w && threadIdx.x == 0) extra_out[row] = 1.0f / (1.0f + expf(-z_s[E]));
+  float mx = -INFINITY;
+  for (int e = threadIdx.x; e < E; e += 128) mx = fmaxf(mx, z_s[e]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float sum = 0.0f;
+  for (int e = threadIdx.x; e < E; e += 128) {
+    const float ex = expf(z_s[e] - mx);
+    z_s[e] = ex;
+    sum += ex;
+  }
+  sum = block_sum<128>(sum, red);
+  for (int e = threadIdx.x; e < E; e += 128) {
+    const float p = z_s[e] / sum;
+    z_s[e] = p;
+    c_s[e] = p + (correction ? correction[e] : 0.0f);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (n_groups > 1 && keep_groups < n_groups) {
+      const int gs = E / n_groups;
+      // drop the worst n_groups - keep_groups runs: repeatedly find the live run with the smallest score (the last
+      // index loses a tie, as the first index wins among the kept)
+      for (int g = 0; g < n_groups; ++g) dead[g] = 0;
+      for (int k = 0; k < n_groups - keep_groups; ++k) {
+        int worst = -1;
+        float wz = INFINITY;
+        for (int g = 0; g < n_groups; ++g) {
+          if (dead[g]) continue;
+          float best = -INFINITY;
+          for (int e = g * gs; e < (g + 1) * gs; ++e) best = fmaxf(best, c_s[e]);
+          if (best <= wz) { wz = best; worst = g; }
+        }
+        dead[worst] = 1;
+      }
+      for (int g = 0; g < n_groups; ++g)
+        if (dead[g])
+          for (int e = g * gs; e < (g + 1) * gs; ++e) c_s[e] = -INFINITY;
+    }
+    float chosen = 0.0f;
+    for (int k = 0; k < top; ++k) {        // the kept groups hold at least `top` outputs, all with finite scores
+      int best = 0;
+      float bz = -INFINITY;
+      for (int e = 0; e < E; ++e) {
+        const float z = c_s[e];
+        if (z > bz) { bz = z; best = e; }
+      }
+      ids[(size_t)row * top + k] = best;
+      weights[(size_t)row * top + k] = z_s[best];
+      chosen += z_s[best];
+      c_s[best] = -INFINITY;
+    }
+    const float inv = 1.0f / (chosen + weight_eps);
+    for (int k = 0; k < top; ++k) weights[(size_t)row * top + k] *= inv;
+  }
+}
+
+// out[row] = sum_k w[row, k] * (ids[row, k] < n_real ? Y[pos_of_pair[row, k]] : h[row])   (outputs from n_real on pass
+// their input through) + addend_gate[row] * addend[row] (a result every token gets, scaled per token)
+template <typename T>
+__global__ void moe_combine_weighted_kernel(T* __restrict__ out, const T* __restrict__ Y, int64_t ldy,
+                                            const int* __restrict__ pos_of_pair, const int* __restrict__ ids,
+                                            const float* __restrict__ pair_w, int n_real, const T* __restrict__ h,
+                                            int64_t ldh, int W, int top, const T* __restrict__ addend, int64_t ld_add,
+                                            const float* __restrict__ addend_gate) {
+  const int row = blockIdx.x;
+  const float ag = addend ? (addend_gate ? addend_gate[row] : 1.0f) : 0.0f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      const size_t p = (size_t)row * top + k;
+      const float v = ids[p] < n_real ? Num<T>::to_f(Y[(size_t)pos_of_pair[p] * ldy + i])
+                                      : Num<T>::to_f(h[(size_t)row * ldh + i]);
+      acc += pair_w[p] * v;
+    }
+    if (addend) acc += ag * Num<T>::to_f(addend[(size_t)row * ld_add + i]);
+    out[(size_t)row * W + i] = Num<T>::from_f(acc);
+  }
+}
+
 #define MOE_DISPATCH(dtype, ...)                                                 \
   switch (dtype) {                                                               \
     case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
@@ -402,6 +513,43 @@ int b200_moe_table_route(int32_t* expert_ids, const int32_t* table, const int32_
   moe_table_route_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       expert_ids, table, tokens, n, (int)top, (int)vocab, (int)E);
   B200_LAUNCH_OK("moe_table_route_kernel");
+  return B200_OK;
+}
+
+int b200_moe_route_softmax(int32_t* expert_ids, float* weights, float* extra_out, const void* h, int64_t ldh,
+                           const float* router_weight, const float* correction, const float* extra_weight,
+                           int64_t rows, int64_t W, int64_t E, int64_t top, int64_t n_groups, int64_t keep_groups,
+                           float weight_eps, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(expert_ids && weights && h && router_weight && (!extra_weight || extra_out),
+                 "moe_route_softmax: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldh >= W && E >= 1 && E <= kMaxExperts && top >= 1 && top <= E &&
+                     top <= kMaxTop && n_groups >= 1 && E % n_groups == 0 && keep_groups >= 1 &&
+                     keep_groups <= n_groups && top <= keep_groups * (E / n_groups),
+                 "moe_route_softmax: bad shape (outputs <= 1024 in equal groups, top <= min(32, outputs of the kept "
+                 "groups))");
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (moe_route_softmax_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
+                          expert_ids, weights, extra_out, static_cast<const T*>(h), ldh, router_weight, correction,
+                          extra_weight, (int)W, (int)E, (int)top, (int)n_groups, (int)keep_groups, weight_eps)));
+  B200_LAUNCH_OK("moe_route_softmax_kernel");
+  return B200_OK;
+}
+
+int b200_moe_combine_weighted(void* out, const void* Y, int64_t ldy, const int32_t* pos_of_pair,
+                              const int32_t* expert_ids, const float* pair_weights, int64_t n_real, const void* h,
+                              int64_t ldh, int64_t rows, int64_t W, int64_t top, const void* addend, int64_t ld_add,
+                              const float* addend_gate, int dtype, b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(out && Y && pos_of_pair && expert_ids && pair_weights && h, "moe_combine_weighted: null pointer");
+  B200_CHECK_ARG(rows > 0 && W > 0 && ldy >= W && ldh >= W && top >= 1 && (!addend || ld_add >= W),
+                 "moe_combine_weighted: bad shape");
+  auto st = static_cast<cudaStream_t>(stream);
+  MOE_DISPATCH(dtype, (moe_combine_weighted_kernel<T><<<(unsigned)rows, 128, 0, st>>>(
+                          static_cast<T*>(out), static_cast<const T*>(Y), ldy, pos_of_pair, expert_ids, pair_weights,
+                          (int)n_real, static_cast<const T*>(h), ldh, (int)W, (int)top,
+                          static_cast<const T*>(addend), ld_add, addend_gate)));
+  B200_LAUNCH_OK("moe_combine_weighted_kernel");
   return B200_OK;
 }
 

@@ -11,6 +11,10 @@
 //   softcap   out = cap tanh(in / cap)
 //   glu       out = g sigmoid(slope g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit)
 //   token gate out = gelu_tanh(a) * table[tok, col0 + c]          a per-token learned vector gates a projection
+//   branches  m = 1/2 (a / rms(a) * wa + b / rms(b) * wb)  (or m = a when there is one branch and no branch weight);
+//             x' = x + m / rms(m) * w ;  h = x' / rms(x') * w_next (or x' itself)   two sublayers side by side whose
+//             normalised results are averaged, normalised again into the residual, and the next sublayer's input norm
+//   relu^2    out = max(in, 0)^2
 //
 // The residual, the history, sums of squares and every transcendental are fp32; T is the activation type
 // of y and of the copy of the residual that the next matrix product reads.
@@ -330,6 +334,79 @@ group_rms_norm_kernel(T* __restrict__ out, const float* __restrict__ x, const fl
   __syncthreads();
   for (int i = threadIdx.x; i < W; i += kRowThreads)
     out[(size_t)row * W + i] = Num<T>::from_f(x_s[i] * r_s[i / gs] * w[i]);
+}
+
+// One CTA per row: the branch results a (and b) are normalised, averaged, normalised again into the fp32 residual, and
+// the new residual is handed on either as it is or under the next sublayer's input norm.  All sums in fp32.
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+branch_norm_residual_kernel(float* __restrict__ x_out, T* __restrict__ h_out, const float* __restrict__ x_in,
+                            const T* __restrict__ a, int64_t lda, const T* __restrict__ b, int64_t ldb,
+                            const float* __restrict__ wa, const float* __restrict__ wb, const float* __restrict__ w,
+                            const float* __restrict__ w_next, int W, float eps) {
+  extern __shared__ __align__(16) float sm[];
+  float* m_s = sm;          // [W]
+  float* b_s = sm + W;      // [W]
+  __shared__ float red[4][32];
+  const int row = blockIdx.x;
+  float sa = 0.0f, sb = 0.0f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float av = Num<T>::to_f(a[(size_t)row * lda + i]);
+    m_s[i] = av;
+    sa += av * av;
+    if (b) {
+      const float bv = Num<T>::to_f(b[(size_t)row * ldb + i]);
+      b_s[i] = bv;
+      sb += bv * bv;
+    }
+  }
+  float sm2 = 0.0f;
+  if (wa) {
+    sa = block_sum<kRowThreads>(sa, red[0]);
+    const float ra = 1.0f / sqrtf(sa / (float)W + eps);
+    float rb = 0.0f;
+    if (b) {
+      sb = block_sum<kRowThreads>(sb, red[1]);
+      rb = 1.0f / sqrtf(sb / (float)W + eps);
+    }
+    for (int i = threadIdx.x; i < W; i += kRowThreads) {
+      float m = m_s[i] * ra * wa[i];
+      if (b) m = 0.5f * (m + b_s[i] * rb * wb[i]);
+      m_s[i] = m;
+      sm2 += m * m;
+    }
+  } else {
+    sm2 = sa;
+  }
+  sm2 = block_sum<kRowThreads>(sm2, red[2]);
+  const float rm = 1.0f / sqrtf(sm2 / (float)W + eps);
+  float sx = 0.0f;
+  for (int i = threadIdx.x; i < W; i += kRowThreads) {
+    const float r = x_in[(size_t)row * W + i] + m_s[i] * rm * w[i];
+    x_out[(size_t)row * W + i] = r;
+    m_s[i] = r;
+    sx += r * r;
+  }
+  if (!h_out) return;
+  if (w_next) {
+    sx = block_sum<kRowThreads>(sx, red[3]);
+    const float rx = 1.0f / sqrtf(sx / (float)W + eps);
+    for (int i = threadIdx.x; i < W; i += kRowThreads)
+      h_out[(size_t)row * W + i] = Num<T>::from_f(m_s[i] * rx * w_next[i]);
+  } else {
+    for (int i = threadIdx.x; i < W; i += kRowThreads) h_out[(size_t)row * W + i] = Num<T>::from_f(m_s[i]);
+  }
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(T* __restrict__ out, const T* __restrict__ in, int64_t rows, int n, int64_t ld_in) {
+  const int64_t total = rows * n;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / n;
+    const float v = fmaxf(Num<T>::to_f(in[r * ld_in + (idx - r * n)]), 0.0f);
+    out[idx] = Num<T>::from_f(v * v);
+  }
 }
 
 template <typename T>
@@ -657,6 +734,41 @@ int b200_token_gated_gelu(void* out, const void* in, int64_t ld_in, const void* 
                                static_cast<T*>(out), static_cast<const T*>(in), ld_in, static_cast<const T*>(table),
                                ld_table, (int)col0, tokens, rows, (int)n, (int)vocab)));
   B200_LAUNCH_OK("token_gated_gelu_kernel");
+  return B200_OK;
+}
+
+int b200_branch_norm_residual(float* x_out, void* h_out, const float* x_in, const void* a, int64_t lda, const void* b,
+                              int64_t ldb, const float* weight_a, const float* weight_b, const float* weight,
+                              const float* weight_next, int64_t rows, int64_t W, float eps, int dtype,
+                              b200_stream_t stream) {
+  if (rows == 0) return B200_OK;
+  B200_CHECK_ARG(x_out && x_in && a && weight, "branch_norm_residual: null pointer");
+  B200_CHECK_ARG(!b || (weight_a && weight_b), "branch_norm_residual: two branches take both branch weights");
+  B200_CHECK_ARG(rows > 0 && W > 0 && lda >= W && (!b || ldb >= W) && 2 * W * 4 <= 200 * 1024,
+                 "branch_norm_residual: bad shape (at most ~25K channels)");
+  auto st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)2 * W * sizeof(float);
+  POSTNORM_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      B200_CUDA_OK(cudaFuncSetAttribute(branch_norm_residual_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
+    branch_norm_residual_kernel<T><<<(unsigned)rows, kRowThreads, smem, st>>>(
+        x_out, static_cast<T*>(h_out), x_in, static_cast<const T*>(a), lda, static_cast<const T*>(b), ldb, weight_a,
+        weight_b, weight, weight_next, (int)W, eps);
+  });
+  B200_LAUNCH_OK("branch_norm_residual_kernel");
+  return B200_OK;
+}
+
+int b200_relu_squared(void* out, const void* in, int64_t rows, int64_t n, int64_t ld_in, int dtype,
+                      b200_stream_t stream) {
+  if (rows == 0 || n == 0) return B200_OK;
+  B200_CHECK_ARG(out && in, "relu_squared: null pointer");
+  B200_CHECK_ARG(rows > 0 && n > 0 && n < (1ll << 30) && ld_in >= n, "relu_squared: bad shape");
+  auto st = static_cast<cudaStream_t>(stream);
+  POSTNORM_DISPATCH(dtype, (relu_squared_kernel<T><<<ew_grid(rows * n), 256, 0, st>>>(
+                               static_cast<T*>(out), static_cast<const T*>(in), rows, (int)n, ld_in)));
+  B200_LAUNCH_OK("relu_squared_kernel");
   return B200_OK;
 }
 

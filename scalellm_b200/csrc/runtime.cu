@@ -61,7 +61,7 @@ tensor_map_encode_fn get_tensor_map_encode() {
 
 extern "C" {
 
-int b200_abi_version(void) { return 2; }
+int b200_abi_version(void) { return 3; }
 
 const char* b200_last_error(void) { return b200::g_err; }
 

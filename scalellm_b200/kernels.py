@@ -1287,3 +1287,189 @@ def sink_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, r1:
                              _p(kv_cu), _p(block_tables), _p(cu_block_lens), _p(token_seq), rows, H, G, dim, vdim,
                              block_size, scale, _dt(k_cache), _stream()))
     return out
+
+
+# ---------------------------------------------------------------------------
+# sigmoid attention inside blocks of positions with a head mix (csrc/sigmoid_attn.cu)
+# ---------------------------------------------------------------------------
+def sigmoid_attn_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_bias: Optional[torch.Tensor],
+                         k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor], k_cache: torch.Tensor,
+                         v_cache: torch.Tensor, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                         slots: torch.Tensor, H: int, G: int, dim: int, vdim: int, rot_dims: int) -> torch.Tensor:
+    """Biased, turned queries as fp32 [rows, H, dim]; biased, turned keys and biased values go to the cache rows
+    `slots`.  The turn pairs channel t with t + rot_dims / 2 of every head (angle position * inv_freq[t]).
+    q_in, k_in, v_in: column blocks of one projection matrix; biases fp32 or None."""
+    _cuda(q_in, k_in, v_in, k_cache, v_cache, q_bias, k_bias, v_bias, inv_freq)
+    _f32(q_bias, k_bias, v_bias, inv_freq)
+    _check_i32(positions, slots)
+    rows, ld = q_in.shape[0], q_in.stride(0)
+    assert q_in.stride(1) == 1 and q_in.shape[1] == H * dim and k_in.shape[1] == G * dim and v_in.shape[1] == G * vdim
+    assert k_in.stride(0) == ld and v_in.stride(0) == ld and k_in.dtype == v_in.dtype == q_in.dtype
+    assert k_in.stride(1) == 1 and v_in.stride(1) == 1
+    assert k_cache.dtype == v_cache.dtype == q_in.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1:] == (G, dim) and v_cache.shape[1:] == (G, vdim)
+    assert rot_dims == 0 or (inv_freq is not None and inv_freq.numel() == rot_dims // 2)
+    q = torch.empty((rows, H, dim), dtype=torch.float32, device=q_in.device)
+    check(_lib.load().b200_sigmoid_attn_prepare(_p(q), _p(q_in), _p(k_in), _p(v_in), ld, _p(q_bias), _p(k_bias),
+                                                _p(v_bias), _p(k_cache), _p(v_cache), _p(inv_freq), _p(positions),
+                                                _p(slots), rows, H, G, dim, vdim, rot_dims, _dt(q_in), _stream()))
+    return q
+
+
+def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, head_bias: Optional[torch.Tensor],
+                 head_mix: Optional[torch.Tensor], q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor,
+                 cu_block_lens: torch.Tensor, token_seq: torch.Tensor, block_size: int, scale: float, cap: float,
+                 size: int, q_max: int = 1) -> torch.Tensor:
+    """[rows, H * vdim] in the cache's dtype: out_h = sum_j a'_hj v_j over the keys j <= i of row i's block of `size`
+    positions (size 0: every j <= i), a_hj = sigmoid(cap tanh(scale q_h . k_j / cap) + head_bias[h]) and
+    a'_h = sum_g head_mix[h, g] a_g (head_bias fp32 [H], head_mix fp32 [H, H], either None).  q_max: the step's
+    longest portion (a host number): CTAs take up to 8 consecutive rows and share their key tiles."""
+    _cuda(q, k_cache, v_cache, head_bias, head_mix)
+    _f32(q, head_bias, head_mix)
+    _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
+    rows, H, dim = q.shape
+    G, vdim = v_cache.shape[1], v_cache.shape[2]
+    assert head_mix is None or head_mix.shape == (H, H)
+    out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
+    check(_lib.load().b200_sigmoid_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(head_bias),
+                                        _p(head_mix), _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens),
+                                        _p(token_seq), rows, H, G, dim, vdim, block_size, scale, cap, size,
+                                        max(1, q_max), _dt(k_cache), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# gated delta rule with short input filters (csrc/delta_rule.cu)
+# ---------------------------------------------------------------------------
+def gated_delta_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, beta_in: torch.Tensor,
+                        decay_in: torch.Tensor, q_filter: torch.Tensor, k_filter: torch.Tensor, v_filter: torch.Tensor,
+                        a_log: torch.Tensor, dt_bias: torch.Tensor, filter_state: torch.Tensor, q_cu: torch.Tensor,
+                        positions: torch.Tensor, token_seq: torch.Tensor, state_slots: torch.Tensor, H: int, G: int,
+                        dim: int, vdim: int, unit_eps: float):
+    """(q [rows, G, dim], k [rows, G, dim], v [rows, H, vdim], decay [rows, H, dim], beta [rows, H]), all fp32:
+    filtered (causal, per channel, `taps` = filter.shape[1] columns, the last one the current token's), silu, q and k
+    of unit length per head and q times dim^(-1/2); decay = exp(-exp(a_log[h]) softplus(decay_in + dt_bias)), beta =
+    sigmoid(beta_in).  filter_state fp32 [n_slots, taps - 1, 2 G dim + H vdim] gives the inputs before the step and
+    takes the step's last ones.  q_in, k_in, v_in, beta_in: column blocks of one matrix."""
+    _cuda(q_in, k_in, v_in, beta_in, decay_in, q_filter, k_filter, v_filter, a_log, dt_bias, filter_state)
+    _f32(q_filter, k_filter, v_filter, a_log, dt_bias, filter_state)
+    _check_i32(q_cu, positions, token_seq, state_slots)
+    rows, ld = q_in.shape[0], q_in.stride(0)
+    taps = q_filter.shape[1]
+    nqk, nv = G * dim, H * vdim
+    for t, n in ((q_in, nqk), (k_in, nqk), (v_in, nv), (beta_in, H)):
+        assert t.shape == (rows, n) and t.stride(1) == 1 and t.stride(0) == ld and t.dtype == q_in.dtype
+    assert decay_in.shape == (rows, H * dim) and decay_in.stride(1) == 1 and decay_in.dtype == q_in.dtype
+    assert q_filter.shape == (nqk, taps) and k_filter.shape == (nqk, taps) and v_filter.shape == (nv, taps)
+    assert a_log.numel() == H and dt_bias.numel() == H * dim
+    assert filter_state.dim() == 3 and filter_state.shape[1:] == (max(taps - 1, 0), 2 * nqk + nv)
+    dev = q_in.device
+    q = torch.empty((rows, G, dim), dtype=torch.float32, device=dev)
+    k = torch.empty((rows, G, dim), dtype=torch.float32, device=dev)
+    v = torch.empty((rows, H, vdim), dtype=torch.float32, device=dev)
+    decay = torch.empty((rows, H, dim), dtype=torch.float32, device=dev)
+    beta = torch.empty((rows, H), dtype=torch.float32, device=dev)
+    check(_lib.load().b200_gated_delta_prepare(_p(q), _p(k), _p(v), _p(decay), _p(beta), _p(q_in), _p(k_in), _p(v_in),
+                                               _p(beta_in), ld, _p(decay_in), decay_in.stride(0), _p(q_filter),
+                                               _p(k_filter), _p(v_filter), _p(a_log), _p(dt_bias), _p(filter_state),
+                                               _p(q_cu), _p(positions), _p(token_seq), _p(state_slots), rows,
+                                               state_slots.numel(), H, G, dim, vdim, taps, unit_eps, _dt(q_in),
+                                               _stream()))
+    return q, k, v, decay, beta
+
+
+def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor,
+                     gate_logits: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor, q_cu: torch.Tensor,
+                     positions: torch.Tensor, state_slots: torch.Tensor, eps: float) -> torch.Tensor:
+    """The recurrence S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per (sequence, head) over
+    the step's rows in order, state fp32 [n_slots, H, dim, vdim] updated in place; returns
+    o / rms(o) * norm_weight * sigmoid(gate_logits) as [rows, H * vdim] in gate_logits' dtype."""
+    _cuda(q, k, v, decay, beta, gate_logits, norm_weight, state)
+    _f32(q, k, v, decay, beta, norm_weight, state)
+    _check_i32(q_cu, positions, state_slots)
+    rows, G, dim = q.shape
+    H, vdim = v.shape[1], v.shape[2]
+    assert k.shape == q.shape and decay.shape == (rows, H, dim) and beta.shape == (rows, H)
+    assert gate_logits.shape == (rows, H * vdim) and gate_logits.stride(1) == 1
+    assert norm_weight.numel() == vdim and state.shape[1:] == (H, dim, vdim)
+    out = torch.empty((rows, H * vdim), dtype=gate_logits.dtype, device=q.device)
+    check(_lib.load().b200_gated_delta_scan(_p(out), H * vdim, _p(q), _p(k), _p(v), _p(decay), _p(beta),
+                                            _p(gate_logits), gate_logits.stride(0), _p(norm_weight), _p(state),
+                                            _p(q_cu), _p(positions), _p(state_slots), state_slots.numel(), H, G, dim,
+                                            vdim, eps, _dt(gate_logits), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# softmax router with group limits and pass-through outputs; branch norms; squared ReLU (csrc/moe.cu, postnorm.cu)
+# ---------------------------------------------------------------------------
+def moe_route_softmax(h: torch.Tensor, router_weight: torch.Tensor, correction: Optional[torch.Tensor], top: int,
+                      n_groups: int = 1, keep_groups: int = 1, weight_eps: float = 0.0,
+                      extra_weight: Optional[torch.Tensor] = None):
+    """(ids [rows, top] int32, weights [rows, top] fp32, extra [rows] fp32 or None): p = softmax(router_weight h) in
+    fp32; the `top` largest p + correction among the outputs of the keep_groups best of n_groups equal runs of
+    neighbours (a run's score: its largest p + correction) are chosen; weights are their p over the sum of the chosen
+    p (+ weight_eps).  extra = sigmoid(extra_weight . h) when extra_weight (fp32 [W]) is given."""
+    _cuda(h, router_weight, correction, extra_weight)
+    _f32(router_weight, correction, extra_weight)
+    rows, W = h.shape
+    E = router_weight.shape[0]
+    assert h.stride(1) == 1 and router_weight.shape[1] == W
+    assert correction is None or correction.numel() == E
+    ids = torch.empty((rows, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((rows, top), dtype=torch.float32, device=h.device)
+    extra = torch.empty(rows, dtype=torch.float32, device=h.device) if extra_weight is not None else None
+    check(_lib.load().b200_moe_route_softmax(_p(ids), _p(wts), _p(extra), _p(h), h.stride(0), _p(router_weight),
+                                             _p(correction), _p(extra_weight), rows, W, E, top, n_groups, keep_groups,
+                                             weight_eps, _dt(h), _stream()))
+    return ids, wts, extra
+
+
+def moe_combine_weighted(y: torch.Tensor, pos_of_pair: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                         n_real: int, h: torch.Tensor, addend: Optional[torch.Tensor] = None,
+                         addend_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[row] = sum_k weights[row, k] * (ids[row, k] < n_real ? y[pos_of_pair[row, k]] : h[row])
+    (+ addend_gate[row] * addend[row])."""
+    _cuda(y, h, addend, addend_gate)
+    _check_i32(pos_of_pair, ids)
+    _f32(weights, addend_gate)
+    rows, top = ids.shape
+    W = h.shape[1]
+    assert y.dim() == 2 and y.stride(1) == 1 and y.shape[1] == W and h.stride(1) == 1 and y.dtype == h.dtype
+    assert pos_of_pair.numel() == rows * top and weights.shape == (rows, top) and weights.is_contiguous()
+    assert addend is None or (addend.shape == (rows, W) and addend.stride(1) == 1 and addend.dtype == y.dtype)
+    out = torch.empty((rows, W), dtype=y.dtype, device=y.device)
+    check(_lib.load().b200_moe_combine_weighted(_p(out), _p(y), y.stride(0), _p(pos_of_pair), _p(ids), _p(weights),
+                                                n_real, _p(h), h.stride(0), rows, W, top, _p(addend),
+                                                addend.stride(0) if addend is not None else 0, _p(addend_gate),
+                                                _dt(y), _stream()))
+    return out
+
+
+def branch_norm_residual(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], weight_a: Optional[torch.Tensor],
+                         weight_b: Optional[torch.Tensor], weight: torch.Tensor, weight_next: Optional[torch.Tensor],
+                         eps: float, x_out: Optional[torch.Tensor] = None, want_h: bool = True):
+    """m = (norm(a) weight_a + norm(b) weight_b) / 2 (one branch: norm(a) weight_a; no branch weight: a itself);
+    x_out (default: x, in place) = x + norm(m) weight; h = norm(x_out) weight_next, or x_out itself without
+    weight_next, in a's dtype.  norm(z) = z / sqrt(mean(z^2) + eps).  Returns (x_out, h or None)."""
+    _cuda(x, a, b, weight_a, weight_b, weight, weight_next)
+    _f32(x, weight_a, weight_b, weight, weight_next)
+    rows, W = x.shape
+    assert a.shape == (rows, W) and a.stride(1) == 1
+    assert b is None or (b.shape == (rows, W) and b.stride(1) == 1 and b.dtype == a.dtype)
+    out = x if x_out is None else x_out
+    _f32(out)
+    h = torch.empty((rows, W), dtype=a.dtype, device=x.device) if want_h else None
+    check(_lib.load().b200_branch_norm_residual(_p(out), _p(h), _p(x), _p(a), a.stride(0), _p(b),
+                                                b.stride(0) if b is not None else 0, _p(weight_a), _p(weight_b),
+                                                _p(weight), _p(weight_next), rows, W, eps, _dt(a), _stream()))
+    return out, h
+
+
+def relu_squared(x: torch.Tensor) -> torch.Tensor:
+    """max(x, 0)^2 of a [rows, n] matrix (rows may be strided)."""
+    _cuda(x)
+    assert x.dim() == 2 and x.stride(1) == 1
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    check(_lib.load().b200_relu_squared(_p(out), _p(x), x.shape[0], x.shape[1], x.stride(0), _dt(x), _stream()))
+    return out

@@ -904,14 +904,14 @@ class ClampedGLU:
         self.gate_up, self.down = Linear(torch.cat([gate, up], dim=0)), Linear(down)
         self.limit, self.slope = limit, slope
 
-    def forward(self, h: torch.Tensor):
-        """The result, or the down projection's split-K partials where the post-norm can take them."""
+    def forward(self, h: torch.Tensor, fusable_out: bool = True):
+        """The result, or (fusable_out) the down projection's split-K partials where the post-norm can take them."""
         gu = self.gate_up.forward_fusable(h)
         if isinstance(gu, kernels.W4Partials):
             act = kernels.glu_clamped_splitk(gu, self.limit, self.slope, h.dtype)
         else:
             act = kernels.glu_clamped(gu, self.limit, self.slope)
-        return self.down.forward_fusable(act)
+        return self.down.forward_fusable(act) if fusable_out else self.down(act)
 
     __call__ = forward
 
@@ -1029,5 +1029,197 @@ class TableMoE:
         y = kernels.grouped_gemm(kernels.gated_act(gu, self.act), self.down, offsets, n)
         return kernels.moe_combine(y, pos_of_pair, rows, self.top, 1.0 / self.top,
                                    self.shared(h) if self.shared is not None else None)
+
+    __call__ = forward
+
+
+# ---------------------------------------------------------------------------
+# Layers of decoders that run two mixers side by side on the same rows (sigmoid attention inside blocks of positions
+# with a head mix, and a gated delta rule with short input filters), average their normalised results, and route
+# tokens to experts with a softmax router under group limits.
+# ---------------------------------------------------------------------------
+class BranchNormResidual:
+    """x <- x + norm(m) w on an fp32 residual, where m is a sublayer's result, or the average of two results each
+    normalised with its own weight first: m = (norm(a) wa + norm(b) wb) / 2.  norm(z) = z / sqrt(mean(z^2) + eps).
+    The new residual is handed on under the next sublayer's input norm (next_weight) or as it is."""
+
+    def __init__(self, weight: torch.Tensor, eps: float, weight_a: Optional[torch.Tensor] = None,
+                 weight_b: Optional[torch.Tensor] = None):
+        f = lambda t: None if t is None else t.to(torch.float32).contiguous()
+        self.weight, self.weight_a, self.weight_b, self.eps = f(weight), f(weight_a), f(weight_b), eps
+
+    def forward(self, x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+                next_weight: Optional[torch.Tensor] = None, want_h: bool = True):
+        """Returns (new x fp32, the rows the next matrix product reads in a's dtype, or None if not wanted)."""
+        return kernels.branch_norm_residual(x, a, b, self.weight_a, self.weight_b if b is not None else None,
+                                            self.weight, next_weight, self.eps, want_h=want_h)
+
+    __call__ = forward
+
+
+class SigmoidBlockAttention:
+    """Attention whose weights are sigmoids, not a softmax (csrc/sigmoid_attn.cu):
+        q, k, v = affine maps of h (biases "q.b", "k.b", "v.b", optional); the first rot_dims channels of every q and
+        k head turn with the position (channel t with t + rot_dims / 2, angle p * inv_freq[t]);
+        s = cap tanh(scale q . k / cap) (cap 0: none); a_h(i, j) = sigmoid(s + pb_h) for the keys j <= i of i's block
+        of `size` positions counted from 0 (size 0: all j <= i); a'_h = sum_g talk[h, g] a_g (no "talk": a' = a);
+        out = Wo concat_h(sum_j a'_h(i, j) v_kv(h)(j)),  H / G query heads per key/value head.
+    `in_weight` [n_in, W] is everything that reads h, so a caller with other mixers on the same rows can make one
+    matrix product of them and hand this mixer its column block (run)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 cap: float, size: int, inv_freq: Optional[torch.Tensor], rot_dims: int, dtype: torch.dtype, device):
+        self.H, self.G, self.dim, self.vd = n_heads, n_kv_heads, dim, vdim
+        self.scale, self.cap, self.size, self.rot_dims, self.dtype = scale, cap, size, rot_dims, dtype
+        self.inv_freq = None if inv_freq is None else inv_freq.to(torch.float32).to(device).contiguous()
+        self.in_weight = torch.cat([w["q"], w["k"], w["v"]], dim=0)
+        self.n_in = self.in_weight.shape[0]
+        self.q_end = n_heads * dim
+        self.k_end = self.q_end + n_kv_heads * dim
+        f = lambda name: w[name].to(torch.float32).to(device).contiguous() if name in w else None
+        self.q_bias, self.k_bias, self.v_bias = f("q.b"), f("k.b"), f("v.b")
+        self.head_bias, self.head_mix = f("pb"), f("talk")
+        self.o_proj = Linear(w["o"])
+        self._in_proj: Optional[Linear] = None
+
+    def run(self, proj: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters) -> torch.Tensor:
+        """proj [rows, n_in]: this mixer's column block of the input product (without biases)."""
+        q = kernels.sigmoid_attn_prepare(proj[:, : self.q_end], proj[:, self.q_end: self.k_end],
+                                         proj[:, self.k_end: self.n_in], self.q_bias, self.k_bias, self.v_bias,
+                                         cache.key_cache, cache.value_cache, self.inv_freq, positions,
+                                         params.new_cache_slots, self.H, self.G, self.dim, self.vd, self.rot_dims)
+        o = kernels.sigmoid_attn(q, cache.key_cache, cache.value_cache, self.head_bias, self.head_mix,
+                                 params.q_cu_seq_lens, params.kv_cu_seq_lens, params.block_tables,
+                                 params.cu_block_lens, params.token_seq, cache.block_size(), self.scale, self.cap,
+                                 self.size, params.q_max_seq_len)
+        return self.o_proj(o)
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters) -> torch.Tensor:
+        if self._in_proj is None:
+            self._in_proj = Linear(self.in_weight)
+        return self.run(self._in_proj(h), positions, cache, params)
+
+    __call__ = forward
+
+
+class GatedDeltaMixer:
+    """Gated delta rule with a decay per key channel and short causal filters on its inputs (csrc/delta_rule.cu):
+        q, k [G heads x dim], v [H heads x vdim] = silu(filter(W h)), filters [channels, taps] ("q.conv", ...);
+        q, k of unit length per head (unit_eps under the root), q times dim^(-1/2); beta = sigmoid(Wb h) per head;
+        decay = exp(-exp(A_log_h) softplus(a2 (a1 h) + dt_bias)) per head and key channel;
+        S <- diag(decay) S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q      (S [dim, vdim] per head, fp32)
+        out = Wo concat_h(o / rms(o) * norm * sigmoid(g2 (g1 h))),  value head h reads q / k head h / (H / G).
+    Per sequence slot the layer keeps S and the last taps - 1 filter inputs, both fp32.  `in_weight` [n_in, W] is
+    everything that reads h (see SigmoidBlockAttention)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], n_heads: int, n_kv_heads: int, dim: int, vdim: int, unit_eps: float,
+                 eps: float, n_slots: int, dtype: torch.dtype, device):
+        self.H, self.G, self.dim, self.vd = n_heads, n_kv_heads, dim, vdim
+        self.unit_eps, self.eps, self.dtype = unit_eps, eps, dtype
+        self.nqk, self.nv = n_kv_heads * dim, n_heads * vdim
+        self.ra, self.rg = w["a1"].shape[0], w["g1"].shape[0]
+        self.in_weight = torch.cat([w["q"], w["k"], w["v"], w["b"], w["a1"], w["g1"]], dim=0)
+        self.n_in = self.in_weight.shape[0]
+        self.a2, self.g2 = Linear(w["a2"]), Linear(w["g2"])
+        f = lambda t: t.to(torch.float32).to(device).contiguous()
+        self.q_filter, self.k_filter, self.v_filter = f(w["q.conv"]), f(w["k.conv"]), f(w["v.conv"])
+        self.taps = self.q_filter.shape[1]
+        self.a_log, self.dt_bias, self.norm_weight = f(w["A_log"]), f(w["dt_bias"]), f(w["norm"])
+        self.o_proj = Linear(w["o"])
+        self.state = torch.zeros((n_slots, n_heads, dim, vdim), dtype=torch.float32, device=device)
+        self.filter_state = torch.zeros((n_slots, max(self.taps - 1, 0), 2 * self.nqk + self.nv), dtype=torch.float32,
+                                        device=device)
+        self._in_proj: Optional[Linear] = None
+
+    def run(self, proj: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
+        """proj [rows, n_in]: this mixer's column block of the input product."""
+        o0 = 2 * self.nqk + self.nv
+        a1 = proj[:, o0 + self.H: o0 + self.H + self.ra].contiguous()
+        g1 = proj[:, o0 + self.H + self.ra: o0 + self.H + self.ra + self.rg].contiguous()
+        q, k, v, decay, beta = kernels.gated_delta_prepare(
+            proj[:, : self.nqk], proj[:, self.nqk: 2 * self.nqk], proj[:, 2 * self.nqk: o0], proj[:, o0: o0 + self.H],
+            self.a2(a1), self.q_filter, self.k_filter, self.v_filter, self.a_log, self.dt_bias, self.filter_state,
+            params.q_cu_seq_lens, positions, params.token_seq, params.state_slots, self.H, self.G, self.dim, self.vd,
+            self.unit_eps)
+        o = kernels.gated_delta_scan(q, k, v, decay, beta, self.g2(g1), self.norm_weight, self.state,
+                                     params.q_cu_seq_lens, positions, params.state_slots, self.eps)
+        return self.o_proj(o)
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
+        if self._in_proj is None:
+            self._in_proj = Linear(self.in_weight)
+        return self.run(self._in_proj(h), positions, params)
+
+    __call__ = forward
+
+
+class ParallelMixer:
+    """Two mixers side by side on the same rows: an attention-like one with a paged cache (`left`) and a recurrent one
+    with state slots (`right`).  Everything that reads h is ONE matrix product; the results come back as a pair (the
+    caller's BranchNormResidual normalises and averages them)."""
+
+    def __init__(self, left, right):
+        self.left, self.right = left, right
+        self.in_proj = Linear(torch.cat([left.in_weight, right.in_weight], dim=0))
+
+    def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters):
+        proj = self.in_proj(h)
+        n = self.left.n_in
+        return (self.left.run(proj[:, :n], positions, cache, params),
+                self.right.run(proj[:, n:], positions, params))
+
+    __call__ = forward
+
+
+class ReluSquaredMLP:
+    """down(max(up h, 0)^2)."""
+
+    def __init__(self, up: torch.Tensor, down: torch.Tensor):
+        self.up, self.down = Linear(up), Linear(down)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(kernels.relu_squared(self.up(h)))
+
+    __call__ = forward
+
+
+class GroupLimitedMoE:
+    """Token-choice experts behind a softmax router (csrc/moe.cu):
+        p = softmax(R h) in fp32 over n_real + n_pass outputs; choice score c = p + correction; the outputs form
+        n_groups equal runs of neighbours, a run scores its largest c, and only outputs of the keep_groups best runs
+        can be chosen; the `top` largest c are chosen; weight = p / (sum of the chosen p + weight_eps);
+        out = sum over chosen e of weight_e * expert_e(h), where the last n_pass outputs are pass-through experts
+        (expert(h) = h, no weights) and a real expert is down(g sigmoid(slope g) (u + 1)), g = min(gate h, limit),
+        u = clamp(up h, -limit, limit);  plus sigmoid(w_sg . h) * shared(h) for an expert every token uses.
+    Expert weights are stacked [n_real, ...]; pairs are grouped by output on the device (no host sync); the pairs of
+    pass-through outputs sort after every real expert's and never enter a matrix product."""
+
+    def __init__(self, router: torch.Tensor, correction: Optional[torch.Tensor], gate: torch.Tensor, up: torch.Tensor,
+                 down: torch.Tensor, top: int, n_groups: int, keep_groups: int, limit: float, slope: float,
+                 weight_eps: float, shared: Optional["ClampedGLU"] = None, shared_gate: Optional[torch.Tensor] = None):
+        f = lambda t: None if t is None else t.to(torch.float32).contiguous()
+        self.router, self.correction = f(router), f(correction)
+        self.gate_up = torch.cat([gate, up], dim=1).contiguous()     # [n_real, 2 ff, W]
+        self.down = down.contiguous()                                  # [n_real, W, ff]
+        self.n_out, self.n_real, self.top = router.shape[0], gate.shape[0], top
+        self.n_groups, self.keep_groups = n_groups, keep_groups
+        self.limit, self.slope, self.weight_eps = limit, slope, weight_eps
+        self.shared = shared
+        self.shared_gate = None if shared_gate is None else f(shared_gate.reshape(-1))
+        if self.n_out < self.n_real or self.n_out % max(n_groups, 1):
+            raise ValueError(f"router with {self.n_out} outputs for {self.n_real} experts in {n_groups} groups")
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        rows = h.shape[0]
+        ids, wts, sg = kernels.moe_route_softmax(h, self.router, self.correction, self.top, self.n_groups,
+                                                 self.keep_groups, self.weight_eps,
+                                                 self.shared_gate if self.shared is not None else None)
+        offsets, sorted_pair, pos_of_pair = kernels.moe_plan(ids, self.n_out)
+        real = offsets[: self.n_real + 1]
+        n = rows * self.top
+        gu = kernels.grouped_gemm(h, self.gate_up, real, n, sorted_pair, None, self.top)
+        y = kernels.grouped_gemm(kernels.glu_clamped(gu, self.limit, self.slope), self.down, real, n)
+        shared = self.shared(h, fusable_out=False) if self.shared is not None else None
+        return kernels.moe_combine_weighted(y, pos_of_pair, ids, wts, self.n_real, h, shared, sg)
 
     __call__ = forward

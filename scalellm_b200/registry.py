@@ -59,4 +59,4 @@ def load_model(model_dir: str, dtype: torch.dtype, device, max_seqs: int = 4):
 
 
 def _import_builtin() -> None:
-    from . import decode_step, kigalix, pokadra, zomurax  # noqa: F401  (their classes register themselves)
+    from . import decode_step, fesupel, kigalix, pokadra, zomurax  # noqa: F401  (their classes register themselves)

@@ -41,7 +41,7 @@ def test_library_exports_every_declared_symbol():
 def test_ctypes_signatures_cover_the_header():
     assert set(_lib.SIGNATURES) == set(header_symbols())
     lib = _lib.load()
-    assert lib.b200_abi_version() == 2
+    assert lib.b200_abi_version() == 3
     assert lib.b200_last_error() is not None
 
 
