@@ -278,3 +278,17 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: torch.Tensor, state: 
         if layer_out is not None:
             layer_out.append(x.clone())
     return norm(x, W["final.norm"], eps) @ W["head"].T
+
+
+class Fesupel:
+    """The functions above bound to one config and one set of weights."""
+
+    def __init__(self, cfg: dict, weights: Dict[str, torch.Tensor], dtype=torch.float64):
+        self.cfg, self.dtype = cfg, dtype
+        self.w = {k: (t.to(dtype) if t.is_floating_point() else t) for k, t in weights.items()}
+
+    def new_state(self) -> dict:
+        return {}
+
+    def forward(self, tokens, state: dict, layer_out: Optional[list] = None) -> torch.Tensor:
+        return forward(self.cfg, self.w, torch.as_tensor(tokens), state, layer_out, self.dtype)

@@ -407,8 +407,8 @@ int b200_gated_delta_prepare(float* q_out, float* k_out, float* v_out, float* de
                              b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(q_out && k_out && v_out && decay_out && beta_out && q_in && k_in && v_in && beta_in && decay_in &&
-                     q_filter && k_filter && v_filter && a_log && dt_bias && filter_state && q_cu_lens && positions &&
-                     token_seq && state_slots,
+                     q_filter && k_filter && v_filter && a_log && dt_bias && (filter_state || taps == 1) && q_cu_lens &&
+                     positions && token_seq && state_slots,
                  "gated_delta_prepare: null pointer");
   B200_CHECK_ARG(rows > 0 && n_seq > 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && dim <= 256 && vdim > 0 &&
                      taps >= 1 && taps <= kMaxTaps,
