@@ -60,9 +60,9 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only; the default is the named config")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
-    ap.add_argument("--arch", default="llama", choices=["llama", "kigalix", "pokadra", "zomurax"],
-                    help="kigalix / pokadra / zomurax: prefill / decode throughput of that design beside the Llama "
-                         "decoder (zomurax also beside kigalix) at equal size through the serving engine (scalellm_b200/arch_bench.py); the default "
+    ap.add_argument("--arch", default="llama", choices=["llama", "kigalix", "pokadra", "zomurax", "fesupel"],
+                    help="kigalix / pokadra / zomurax / fesupel: prefill / decode throughput of that design beside the Llama "
+                         "decoder (zomurax and fesupel also beside kigalix) at equal size through the serving engine (scalellm_b200/arch_bench.py); the default "
                          "workload and its JSON line are untouched")
     ap.add_argument("--arch-size", default="all", choices=["all", "w2048", "w4096"])
     ap.add_argument("--arch-batch", type=int, default=16)
@@ -706,6 +706,10 @@ def main():
     if a.arch == "zomurax":
         from scalellm_b200 import arch_bench
         arch_bench.run_zomurax(a)
+        return
+    if a.arch == "fesupel":
+        from scalellm_b200 import arch_bench
+        arch_bench.run_fesupel(a)
         return
     if a.arch == "pokadra":
         from scalellm_b200 import arch_bench

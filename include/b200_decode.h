@@ -754,6 +754,18 @@ B200_API int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const voi
                                const int32_t* cu_block_lens, const int32_t* token_seq, int64_t rows, int64_t H,
                                int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale, float cap,
                                int64_t size, int64_t rows_per_cta, int dtype, b200_stream_t stream);
+/* The same for prompt portions in bf16 on the tensor cores: tiles of 16 consecutive tokens of a sequence x all heads
+ * (dim and vdim multiples of 16 and shared memory for the heads' queries and one key tile: ..._supported tells);
+ * q_max: the longest portion of the step. */
+B200_API int b200_sigmoid_attn_prefill_supported(int64_t H, int64_t G, int64_t dim, int64_t vdim, int has_mix,
+                                                 int dtype);
+B200_API int b200_sigmoid_attn_prefill(void* out, int64_t ldo, const float* q, const void* k_cache,
+                                       const void* v_cache, const float* head_bias /*nullable*/,
+                                       const float* head_mix /*nullable*/, const int32_t* q_cu_lens,
+                                       const int32_t* kv_cu_lens, const int32_t* block_tables,
+                                       const int32_t* cu_block_lens, int64_t n_seq, int64_t q_max, int64_t H,
+                                       int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale,
+                                       float cap, int64_t size, int dtype, b200_stream_t stream);
 /* Inputs of the gated delta rule for every row: x = silu(filter(x_in)) with causal per-channel filters [channels, taps]
  * (last column: the current token; lags before the step come from filter_state [n_slots, taps - 1, 2 G dim + H vdim],
  * lags before position 0 are zero); q, k [rows, G, dim] made unit length per head (eps unit_eps under the root), q also

@@ -1,6 +1,6 @@
-"""Prefill and decode throughput of the Kigalix, Pokadra and Zomurax designs beside the Llama decoder (Zomurax also
-beside Kigalix, the design nearest to it) at equal size (`bench.py --arch kigalix|pokadra|zomurax`), all through the
-serving engine, random weights, bf16.
+"""Prefill and decode throughput of the Kigalix, Pokadra, Zomurax and Fesupel designs beside the Llama decoder (Zomurax
+and Fesupel also beside Kigalix, the design nearest to them) at equal size (`bench.py --arch
+kigalix|pokadra|zomurax|fesupel`), all through the serving engine, random weights, bf16.
 
 Per size: tokens/s of a prompt step (B sequences of L tokens in one batch) and of decode steps (B sequences
 with L cached tokens, one token each), timed with CUDA events after warm-up; and, per kind of kernel, the
@@ -602,5 +602,205 @@ def run_zomurax(args) -> None:
         out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "zomurax": z, "kigalix": k, "llama": l,
                               "kernel_rooflines": zomurax_rooflines(s, batch, seqlen, z, k, l, peaks),
                               "attention_kernels": zomurax_attention_kernels(s, peaks),
+                              "seconds": round(time.time() - t0, 1)}
+    print(json.dumps(out))
+
+
+# ---------------------------------------------------------------------------
+# Fesupel beside Kigalix (a delta-rule layer, attention layers, routed experts) and Llama
+# ---------------------------------------------------------------------------
+FESUPEL_EXTRA = {"w2048": dict(kv_heads=4, block=512, rheads=16, rkv=8, rdim=128, rvdim=128, taps=4, shared=1408,
+                               identity=2, side=64),
+                 "w4096": dict(kv_heads=8, block=512, rheads=32, rkv=16, rdim=128, rvdim=128, taps=4, shared=2752,
+                               identity=2, side=64)}
+FESUPEL_KERNELS = ["bigram_embed", "group_rms_norm", "branch_norm_residual", "sigmoid_attn_prepare", "sigmoid_attn",
+                   "gated_delta_prepare", "gated_delta_scan", "relu_squared", "glu_clamped", "glu_clamped_splitk",
+                   "moe_route_softmax", "moe_plan", "grouped_gemm", "moe_combine_weighted", "token_side_postnorm",
+                   "token_gated_gelu", "postnorm_residual"]
+
+
+def fesupel_config(s: dict) -> dict:
+    """Every layer runs both mixers; the first feed-forward is dense, the others are routed."""
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"],
+            "mask": {"size": s["block"]}, "scale": s["dim"] ** -0.5, "softcap": 30.0,
+            "rot": {"base": 10000.0, "dims": s["rot"],
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}
+    right = {"heads": s["rheads"], "kv_heads": s["rkv"], "dim": s["rdim"], "vdim": s["rvdim"], "conv": s["taps"]}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "top": s["top"], "identity": s["identity"],
+                      "groups": {"count": 2, "keep": 1}},
+           "shared": {"ff": s["shared"], "limit": 7.0}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Fesupel", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": s["width"] ** 0.5}, "token_side": {"dim": s["side"]},
+            "layers": [{"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense if i == 0 else moe}
+                       for i in range(s["layers"])]}
+
+
+def _block_pairs(ctx: int, q_len: int, block: int) -> int:
+    """(query, key) pairs of one sequence with ctx tokens whose last q_len are the step's rows, keys limited to the
+    row's block of `block` positions."""
+    return sum(i % block + 1 if block else i + 1 for i in range(ctx - q_len, ctx))
+
+
+def fesupel_rooflines(s: dict, batch: int, seqlen: int, f: dict, k: dict, l: dict, peaks: dict) -> dict:
+    """Achieved fraction of the nearer roof per kind of kernel, from the per-kernel times of one step of each model
+    (all layers of that kind together), each beside the like kernel of the nearest existing model."""
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    L, W = s["layers"], s["width"]
+    H, G, dim, vd, blk = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["block"]
+    RH, RG, rd, rv = s["rheads"], s["rkv"], s["rdim"], s["rvdim"]
+    k_lat = sum(1 for i in range(L) if i % 4 != 1)
+    k_moe = sum(1 for i in range(L) if i % 4 != 0)
+    Dk = s["rank"] + s["rot"]
+    out = {}
+    for phase in ("decode", "prefill"):
+        q_len = 1 if phase == "decode" else seqlen
+        ctx = seqlen + 1 if phase == "decode" else seqlen
+        rows = batch * q_len
+        fm, km, lm = f[phase]["kernels_ms"], k[phase]["kernels_ms"], l[phase]["kernels_ms"]
+        bpairs = batch * _block_pairs(ctx, q_len, blk)
+        pairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        touched = batch * (min(ctx, (ctx - 1) % blk + 1) if phase == "decode" else ctx)
+        out[f"fesupel sigmoid_attn (blocks of {blk}) {phase}"] = _frac(
+            fm.get("sigmoid_attn", 0.0), L * (touched * G * (dim + vd) * 2 + rows * H * (dim * 4 + vd * 2)),
+            L * bpairs * H * 2 * (dim + vd), hbm, tf)
+        out[f"kigalix latent_attn {phase}"] = _frac(
+            km.get("latent_attn", 0.0), k_lat * (batch * ctx * Dk * 2 + rows * s["heads"] * (Dk + s["rank"]) * 4),
+            k_lat * pairs * s["heads"] * 2 * (Dk + s["rank"]), hbm, tf)
+        Hl, Hkv = W // 128, max(1, W // 512)
+        out[f"llama paged attention {phase}"] = _frac(
+            lm.get("paged_kv_varlen_mha", 0.0), L * (batch * ctx * 2 * Hkv * 128 * 2 + rows * Hl * 128 * 4),
+            L * pairs * Hl * 4 * 128, hbm, tf)
+        # the scan reads q, k, decay (fp32), v (fp32), the gate (16 bits) and writes 16 bits per value channel; the
+        # matrices go in and out once per sequence
+        out[f"fesupel gated_delta_scan {phase}"] = _frac(
+            fm.get("gated_delta_scan", 0.0),
+            L * (rows * (2 * RG * rd * 4 + RH * rd * 4 + RH * rv * 8) + batch * 2 * RH * rd * rv * 4),
+            L * rows * RH * 6 * rd * rv, hbm, tf)
+        n_d, dn = L - k_lat, s["dheads"] * s["ddim"]
+        out[f"kigalix delta_rule {phase}"] = _frac(
+            km.get("delta_rule", 0.0), n_d * (rows * 7 * dn * 2 + batch * 2 * dn * s["ddim"] * 4),
+            n_d * rows * s["dheads"] * 6 * s["ddim"] ** 2, hbm, tf)
+        nch = 2 * RG * rd + RH * rv
+        out[f"fesupel gated_delta_prepare {phase}"] = _frac(
+            fm.get("gated_delta_prepare", 0.0), L * rows * (nch * 2 + RH * rd * 2 + nch * 4 + RH * rd * 4), 0, hbm, tf)
+        out[f"fesupel sigmoid_attn_prepare {phase}"] = _frac(
+            fm.get("sigmoid_attn_prepare", 0.0), L * rows * ((H + G) * dim * 2 + G * vd * 2 + H * dim * 4 + G * (dim + vd) * 2),
+            0, hbm, tf)
+        out[f"kigalix latent_prepare {phase}"] = _frac(
+            km.get("latent_prepare", 0.0), k_lat * rows * (s["heads"] * s["rot"] * 4 + 2 * Dk * 2), 0, hbm, tf)
+        npairs = rows * s["top"]
+        ebytes = s["experts"] * 3 * s["eff"] * W * 2 + npairs * (W * 2 + 3 * s["eff"]) * 2
+        out[f"fesupel expert GEMMs {phase}"] = _frac(fm.get("grouped_gemm", 0.0), (L - 1) * ebytes,
+                                                    (L - 1) * npairs * 6 * s["eff"] * W, hbm, tf)
+        out[f"kigalix expert GEMMs {phase}"] = _frac(km.get("grouped_gemm", 0.0), k_moe * ebytes,
+                                                    k_moe * npairs * 6 * s["eff"] * W, hbm, tf)
+        # branch norms: the mixer's launch reads x (4) and two results (2 + 2), writes x (4) and 16 bits; the
+        # feed-forward's reads x and one result
+        out[f"fesupel branch_norm_residual {phase}"] = _frac(fm.get("branch_norm_residual", 0.0),
+                                                            rows * W * L * (14 + 12), 0, hbm, tf)
+        out[f"llama rms_norm_residual {phase}"] = _frac(
+            lm.get("rms_norm_residual", 0.0) + lm.get("rms_norm", 0.0) + lm.get("rms_norm_residual_splitk", 0.0),
+            rows * W * (2 * L + 1) * 4 * 2, 0, hbm, tf)
+    return out
+
+
+def fesupel_kernels_alone(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 2048))) -> dict:
+    """The design's attention and recurrence kernels alone beside their like kernels (Llama's paged attention with the
+    same heads; Kigalix's delta rule with the same state size), on caches larger than L2: (batch, cached length, new
+    tokens per sequence) = decoding over long contexts and one prompt portion.  CUDA events around 10 launches after
+    3."""
+    from . import kernels
+    from .decode_step import BlockPool, StepBuffers, build_step_batch
+    dev = torch.device("cuda", torch.cuda.current_device())
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    H, G, dim, vd, blk = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["block"]
+    RH, RG, rd, rv = s["rheads"], s["rkv"], s["rdim"], s["rvdim"]
+    bs, out = 16, {}
+    for batch, ctx, q_len in cases:
+        n_blocks = batch * (-(-ctx // bs)) + 8
+        pool = BlockPool(n_blocks, bs, seed=1)
+        seqs = []
+        for _ in range(batch):
+            sq = pool.open_sequence()
+            pool.reserve(sq, ctx)
+            seqs.append(sq)
+        hb = build_step_batch(pool, seqs, [[0] * q_len] * batch, [ctx - q_len] * batch, list(range(batch)))
+        tokens, positions, prm = StepBuffers(dev, batch * q_len, batch, n_blocks).upload(hb)
+        rows = batch * q_len
+        g = torch.Generator(device=dev).manual_seed(0)
+        rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+        r32 = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32)
+        kc, vc = rnd(n_blocks * bs, G, dim), rnd(n_blocks * bs, G, vd)
+        q = r32(rows, H, dim)
+        hbias, mix = r32(H) - 3.0, torch.eye(H, device=dev) + 0.1 * r32(H, H)
+        f_sig = lambda size: (lambda: kernels.sigmoid_attn(q, kc, vc, hbias, mix, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                           prm.block_tables, prm.cu_block_lens, prm.token_seq, bs,
+                                                           dim ** -0.5, 30.0, size, q_len))
+        kl, vl = rnd(n_blocks * bs, G, dim), rnd(n_blocks * bs, G, dim)
+        ql, ol = rnd(rows, H, dim), torch.empty((rows, H, dim), dtype=torch.bfloat16, device=dev)
+        f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kl, vl, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
+                                                      prm.block_tables, prm.cu_block_lens, None, bs, q_len, ctx,
+                                                      dim ** -0.5, 0.0, -1)
+        pairs = batch * _visible_pairs(ctx, q_len, 0, 0)
+        bpairs = batch * _block_pairs(ctx, q_len, blk)
+        touched = batch * ((ctx - 1) % blk + 1 if q_len == 1 else ctx)
+        qb = rows * H * (dim * 4 + vd * 2)
+        # the recurrence: S [rd x rv] per head in and out once per sequence, the rows' inputs once
+        dq, dk = torch.nn.functional.normalize(r32(rows, RG, rd), dim=-1), torch.nn.functional.normalize(r32(rows, RG, rd), dim=-1)
+        dv, dd, db = r32(rows, RH, rv), torch.sigmoid(r32(rows, RH, rd) + 3.0), torch.sigmoid(r32(rows, RH))
+        dg, dn = rnd(rows, RH * rv), torch.ones(rv, device=dev)
+        st = torch.zeros((batch, RH, rd, rv), dtype=torch.float32, device=dev)
+        f_gd = lambda: kernels.gated_delta_scan(dq, dk, dv, dd, db, dg, dn, st, prm.q_cu_seq_lens, positions,
+                                                prm.state_slots, 1e-5)
+        n = RH * rd
+        proj = rnd(rows, 5 * n)
+        wl = rnd(rows, n)
+        w0, a0, nw = r32(n), r32(n), torch.ones(n, device=dev)
+        st2 = torch.zeros((batch, RH, rd, rd), dtype=torch.float32, device=dev)
+        f_kd = lambda: kernels.delta_rule(*(proj[:, i * n:(i + 1) * n] for i in range(3)), wl, proj[:, 3 * n:4 * n],
+                                          proj[:, 4 * n:], w0, a0, nw, st2, prm.q_cu_seq_lens, positions,
+                                          prm.state_slots, RH, rd, 0.6, 1e-6, 1e-5)
+        for name, fn, nbytes, flops in (
+                (f"fesupel sigmoid_attn, blocks of {blk}", f_sig(blk), touched * G * (dim + vd) * 2 + qb,
+                 bpairs * H * 2 * (dim + vd)),
+                ("fesupel sigmoid_attn, no block limit", f_sig(0), batch * ctx * G * (dim + vd) * 2 + qb,
+                 pairs * H * 2 * (dim + vd)),
+                ("llama paged attention, same heads", f_llama, batch * ctx * 2 * G * dim * 2 + rows * H * dim * 4,
+                 pairs * H * 4 * dim),
+                ("fesupel gated_delta_scan", f_gd,
+                 rows * (2 * RG * rd * 4 + RH * rd * 4 + RH * rv * 8) + batch * 2 * RH * rd * rv * 4, rows * RH * 6 * rd * rv),
+                ("kigalix delta_rule, same heads and state", f_kd, rows * 7 * n * 2 + batch * 2 * n * rd * 4,
+                 rows * RH * 6 * rd * rd)):
+            if q_len > 1 and "no block limit" in name:
+                continue            # the walk over every earlier key on CUDA cores is not a prompt kernel
+            ms = _time_steps(fn, 3, 10)
+            out[f"{name}, {batch} x {ctx} cached, {q_len} new"] = _frac(ms, nbytes, flops, hbm, tf)
+        del kc, vc, kl, vl
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_fesupel(args) -> None:
+    torch.cuda.set_device(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peaks = json.load(open(peaks_path)) if os.path.exists(peaks_path) else {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    out = {"metric": "fesupel_vs_kigalix_vs_llama_tokens_per_s", "unit": "tokens/s", "dtype": "bf16",
+           "data": "synthetic (random-init weights, random token ids)", "n_gpus": 1,
+           "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"],
+                     "source": "measured" if os.path.exists(peaks_path) else "fallback"}, "sizes": {}}
+    names = [args.arch_size] if args.arch_size != "all" else list(SIZES)
+    for name in names:
+        s = dict(SIZES[name], **FESUPEL_EXTRA[name])
+        batch, seqlen = args.arch_batch, args.arch_seqlen
+        t0 = time.time()
+        f = _run_model(fesupel_config(s), batch, seqlen, args.warmup, args.steps, FESUPEL_KERNELS)
+        k = _run_model(kigalix_config(s), batch, seqlen, args.warmup, args.steps, KIGALIX_KERNELS)
+        l = _run_model(llama_config(s), batch, seqlen, args.warmup, args.steps, LLAMA_KERNELS)
+        out["sizes"][name] = {"shape": s, "batch": batch, "seq_len": seqlen, "fesupel": f, "kigalix": k, "llama": l,
+                              "kernel_rooflines": fesupel_rooflines(s, batch, seqlen, f, k, l, peaks),
+                              "kernels_alone": fesupel_kernels_alone(s, peaks),
                               "seconds": round(time.time() - t0, 1)}
     print(json.dumps(out))

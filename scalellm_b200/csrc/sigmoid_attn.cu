@@ -192,6 +192,284 @@ sigmoid_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ 
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// Prompt portions in bf16 on the tensor cores (mma.sync m16n8k16, fp32 accumulation).
+// One CTA = 16 warps = 16 consecutive tokens of one sequence x ALL heads x a range of VW value channels (grid z).
+// Keys walk in tiles of 16 from the first key of the first row's block of positions; K [G][16][dim] and the CTA's
+// channels of V [G][16][VW] are copied asynchronously through the block table (two buffers where they fit).  Per tile:
+//   scores   unit = (head, 8 keys): S = Q K^T, scale, cap, head bias, sigmoid; causal and same-block test per
+//            element; the weights go to shared memory in fp32, [head][row][key]
+//   mix      unit = (head, part of its channels): the thread gathers its A-fragment positions of
+//            a'_h = sum_g M[h, g] a_g from shared memory (fp32) and splits them into two bf16 terms (hi + lo)
+//   sum      O_h += a'_h V_g for the unit's channel blocks, both terms
+// The queries are rounded to bf16 like the cached keys; everything after the product is fp32.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int kTW = 16;           // warps per CTA
+constexpr int kTK = 16;           // keys per tile
+constexpr int kAS = kTK + 1;      // row stride of the weights in shared memory
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = smem_u32(smem_dst);
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+  hi = Num<__nv_bfloat16>::pack(__bfloat162float(xh), __bfloat162float(yh));
+  lo = Num<__nv_bfloat16>::pack(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+// UPW: (head, part) units a warp owns in the mix and the sum; NPU: blocks of 16 value channels per unit
+template <int UPW, int NPU>
+__global__ void __launch_bounds__(kTW * 32, 1)
+sigmoid_attn_prefill_kernel(__nv_bfloat16* __restrict__ out, int64_t ldo, const float* __restrict__ q,
+                            const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                            const float* __restrict__ head_bias, const float* __restrict__ head_mix,
+                            const int* __restrict__ q_cu, const int* __restrict__ kv_cu,
+                            const int* __restrict__ block_tables, const int* __restrict__ cu_block_lens, int H, int G,
+                            int dim, int vdim, int block_size, float scale, float cap, int size, int VW, int parts,
+                            int npu, int nbuf) {
+  extern __shared__ __align__(16) unsigned char smraw[];
+  const int KROW = dim + 8, VROW = VW + 8;               // bf16 elements per staged row (16 bytes of padding)
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smraw);          // [H][16][KROW]
+  __nv_bfloat16* Ks = Qs + (size_t)H * 16 * KROW;                       // [nbuf][G][kTK][KROW] (+ 16 elements slack)
+  __nv_bfloat16* Vs = Ks + (size_t)nbuf * G * kTK * KROW + 16;          // [nbuf][G][kTK][VROW]
+  float* a_s = reinterpret_cast<float*>(Vs + (size_t)nbuf * G * kTK * VROW);   // [H][16][kAS]
+  float* mix_s = a_s + (size_t)H * 16 * kAS;                            // [H][H]
+  float* hb_s = mix_s + (head_mix ? H * H : 0);                         // [H]
+  const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = q_cu[seq], q_len = q_cu[seq + 1] - q0, kv_len = kv_cu[seq + 1] - kv_cu[seq];
+  const int t0 = blockIdx.x * 16;                        // first token of the CTA within the step's portion
+  if (t0 >= q_len) return;
+  const int R = H / G, KS = dim / 16;
+  const int ch0 = blockIdx.z * VW;                       // first value channel of this CTA
+  const int P0 = kv_len - q_len + t0;                    // position of the CTA's first row
+  const int n_rows = min(16, q_len - t0);
+  const int P1 = P0 + n_rows - 1;
+  const int jb = size > 0 ? (P0 / size) * size : 0;      // first key any row of the CTA sees
+  const int n_tiles = (P1 - jb) / kTK + 1;
+  const int* table = block_tables + cu_block_lens[seq];
+  if (head_mix)
+    for (int i = threadIdx.x; i < H * H; i += kTW * 32) mix_s[i] = head_mix[i];
+  for (int i = threadIdx.x; i < H; i += kTW * 32) hb_s[i] = head_bias ? head_bias[i] : 0.0f;
+  for (int e = threadIdx.x; e < H * 16 * dim; e += kTW * 32) {
+    const int d = e % dim, rh = e / dim, rr = rh % 16, h = rh / 16;
+    const float v = rr < n_rows ? q[((size_t)(q0 + t0 + rr) * H + h) * dim + d] : 0.0f;
+    Qs[((size_t)h * 16 + rr) * KROW + d] = __float2bfloat16_rn(v);
+  }
+  const size_t k_stride = (size_t)G * dim, v_stride = (size_t)G * vdim;
+  const int kchunks = dim / 8, vchunks = VW / 8;
+  auto load_tile = [&](int idx, int buf) {
+    const int per_row = kchunks + vchunks;
+    for (int e = threadIdx.x; e < G * kTK * per_row; e += kTW * 32) {
+      const int c = e % per_row, gk = e / per_row, key = gk % kTK, g = gk / kTK;
+      const int j = jb + idx * kTK + key;
+      const bool ok = j <= P1;
+      size_t slot = 0;
+      if (ok) slot = (size_t)table[j / block_size] + j % block_size;
+      if (c < kchunks)
+        cp_async16(Ks + (((size_t)buf * G + g) * kTK + key) * KROW + c * 8,
+                   k_cache + slot * k_stride + (size_t)g * dim + c * 8, ok);
+      else
+        cp_async16(Vs + (((size_t)buf * G + g) * kTK + key) * VROW + (c - kchunks) * 8,
+                   v_cache + slot * v_stride + (size_t)g * vdim + ch0 + (c - kchunks) * 8, ok);
+    }
+  };
+  load_tile(0, 0);
+  cp_async_commit();
+
+  const int gr = lane >> 2, qc = (lane & 3) * 2;         // fragment row within 8, first column of the pair
+  int pos[2], blk0[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int rr = gr + r * 8;
+    pos[r] = rr < n_rows ? P0 + rr : -1;
+    blk0[r] = (size > 0 && pos[r] >= 0) ? (pos[r] / size) * size : 0;
+  }
+  float o[UPW][NPU * 2][4];
+#pragma unroll
+  for (int u = 0; u < UPW; ++u)
+#pragma unroll
+    for (int n = 0; n < NPU * 2; ++n) o[u][n][0] = o[u][n][1] = o[u][n][2] = o[u][n][3] = 0.0f;
+  const int n_units = H * parts;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int buf = nbuf == 2 ? (it & 1) : 0;
+    cp_async_wait_all();
+    __syncthreads();                                     // tile `it` has landed; everyone is done with tile it - 1
+    if (nbuf == 2 && it + 1 < n_tiles) {
+      load_tile(it + 1, buf ^ 1);
+      cp_async_commit();
+    }
+    const int j0 = jb + it * kTK;
+    const __nv_bfloat16* kt = Ks + (size_t)buf * G * kTK * KROW;
+    const __nv_bfloat16* vt = Vs + (size_t)buf * G * kTK * VROW;
+    // scores: unit = (head, half of the tile's keys)
+    for (int u = warp; u < H * 2; u += kTW) {
+      const int h = u >> 1, nt = u & 1;
+      const __nv_bfloat16* qh = Qs + (size_t)h * 16 * KROW;
+      const __nv_bfloat16* kg = kt + (size_t)(h / R) * kTK * KROW;
+      float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (int ks = 0; ks < KS; ks += 2) {
+        uint32_t a[4], b[4];
+        ldsm_x4(b, kg + (nt * 8 + (lane & 7)) * KROW + ks * 16 + (lane >> 3) * 8);
+        ldsm_x4(a, qh + (lane & 15) * KROW + ks * 16 + (lane >> 4) * 8);
+        mma_bf16(sc, a, b[0], b[1]);
+        if (ks + 1 < KS) {
+          ldsm_x4(a, qh + (lane & 15) * KROW + (ks + 1) * 16 + (lane >> 4) * 8);
+          mma_bf16(sc, a, b[2], b[3]);
+        }
+      }
+      const float hb = hb_s[h];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int j = j0 + nt * 8 + qc + (e & 1);
+        float w = 0.0f;
+        if (j <= pos[r] && j >= blk0[r]) {
+          float v = sc[e] * scale;
+          if (cap > 0.0f) v = cap * tanhf(v / cap);
+          w = sigmoidf_(v + hb);
+        }
+        a_s[((size_t)h * 16 + gr + r * 8) * kAS + nt * 8 + qc + (e & 1)] = w;
+      }
+    }
+    __syncthreads();
+    // mix and weighted sum: unit = (head, part of the CTA's channels)
+#pragma unroll
+    for (int uu = 0; uu < UPW; ++uu) {
+      const int u = warp + uu * kTW;
+      if (u < n_units) {
+        const int h = u / parts, part = u - h * parts;
+        float m[8];                                       // (row gr | gr + 8) x (keys qc, qc + 1 | qc + 8, qc + 9)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m[i] = 0.0f;
+        if (head_mix) {
+          for (int g2 = 0; g2 < H; ++g2) {
+            const float t = mix_s[h * H + g2];
+            const float* ar = a_s + (size_t)g2 * 16 * kAS;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              m[i] += t * ar[(gr + ((i >> 1) & 1) * 8) * kAS + qc + (i & 1) + (i >> 2) * 8];
+          }
+        } else {
+          const float* ar = a_s + (size_t)h * 16 * kAS;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) m[i] = ar[(gr + ((i >> 1) & 1) * 8) * kAS + qc + (i & 1) + (i >> 2) * 8];
+        }
+        uint32_t phi[4], plo[4];
+        split_bf16(m[0], m[1], phi[0], plo[0]);           // a0: row gr, keys qc..
+        split_bf16(m[2], m[3], phi[1], plo[1]);           // a1: row gr + 8
+        split_bf16(m[4], m[5], phi[2], plo[2]);           // a2: row gr, keys qc + 8..
+        split_bf16(m[6], m[7], phi[3], plo[3]);           // a3: row gr + 8
+        const __nv_bfloat16* vg = vt + (size_t)(h / R) * kTK * VROW;
+        const __nv_bfloat16* vrow = vg + ((lane & 7) + ((lane >> 3) & 1) * 8) * VROW + (lane >> 4) * 8;
+#pragma unroll
+        for (int n = 0; n < NPU; ++n) {
+          const int cb = part * npu + n;                  // block of 16 channels within the CTA's range
+          if (n < npu && cb * 16 < VW) {
+            uint32_t b[4];
+            ldsm_x4_t(b, vrow + cb * 16);
+            mma_bf16(o[uu][n * 2], phi, b[0], b[1]);
+            mma_bf16(o[uu][n * 2 + 1], phi, b[2], b[3]);
+            mma_bf16(o[uu][n * 2], plo, b[0], b[1]);
+            mma_bf16(o[uu][n * 2 + 1], plo, b[2], b[3]);
+          }
+        }
+      }
+    }
+    if (nbuf == 1 && it + 1 < n_tiles) {
+      __syncthreads();                                   // the single buffer is free again
+      load_tile(it + 1, 0);
+      cp_async_commit();
+    }
+  }
+  cp_async_wait_all();
+#pragma unroll
+  for (int uu = 0; uu < UPW; ++uu) {
+    const int u = warp + uu * kTW;
+    if (u >= n_units) continue;
+    const int h = u / parts, part = u - h * parts;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (pos[r] < 0) continue;
+      __nv_bfloat16* dst = out + (size_t)(q0 + t0 + gr + r * 8) * ldo + (size_t)h * vdim + ch0;
+#pragma unroll
+      for (int n = 0; n < NPU * 2; ++n) {
+        const int c = (part * npu + (n >> 1)) * 16 + (n & 1) * 8 + qc;
+        if ((n >> 1) < npu && c < VW)
+          *reinterpret_cast<uint32_t*>(dst + c) = Num<__nv_bfloat16>::pack(o[uu][n][r * 2], o[uu][n][r * 2 + 1]);
+      }
+    }
+  }
+}
+
+struct PrefillPlan {
+  int zs, VW, parts, npu, upw, nbuf;
+  size_t smem;
+  bool ok;
+};
+
+// The channel split over CTAs, the (head, part) units and the buffers that fit: at most 8 blocks of 16 channels per
+// warp (64 accumulator registers), shared memory within the opt-in limit.
+inline PrefillPlan plan_prefill(int H, int G, int dim, int vdim, bool mix) {
+  PrefillPlan p{};
+  p.ok = false;
+  if (dim % 16 || vdim % 16 || H % G || dim > 256) return p;
+  for (int zs = 1; zs <= 8; zs *= 2) {
+    if (vdim % (16 * zs)) break;
+    const int VW = vdim / zs, nth = VW / 16;
+    int parts = 1;
+    while (parts * 2 * H <= kTW && parts * 2 <= nth) parts *= 2;
+    const int npu = (nth + parts - 1) / parts;
+    const int upw = (H * parts + kTW - 1) / kTW;
+    if (upw * npu > 8 || upw > 4) continue;
+    for (int nbuf = 2; nbuf >= 1; --nbuf) {
+      const size_t smem = ((size_t)H * 16 * (dim + 8) + (size_t)nbuf * G * kTK * (dim + 8) + 16 +
+                           (size_t)nbuf * G * kTK * (VW + 8)) * 2 +
+                          ((size_t)H * 16 * kAS + (mix ? (size_t)H * H : 0) + H) * 4;
+      if (smem <= 227 * 1024) {
+        p = PrefillPlan{zs, VW, parts, npu, upw, nbuf, smem, true};
+        return p;
+      }
+    }
+  }
+  return p;
+}
+
+template <int UPW, int NPU>
+int launch_prefill(const PrefillPlan& p, void* out, int64_t ldo, const float* q, const void* kc, const void* vc,
+                   const float* hb, const float* mix, const int* q_cu, const int* kv_cu, const int* bt, const int* cbl,
+                   int64_t n_seq, int64_t q_max, int H, int G, int dim, int vdim, int bs, float scale, float cap,
+                   int size, cudaStream_t st) {
+  auto kern = sigmoid_attn_prefill_kernel<UPW, NPU>;
+  if (p.smem > 48 * 1024)
+    B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
+  dim3 grid((unsigned)((q_max + 15) / 16), (unsigned)n_seq, (unsigned)p.zs);
+  kern<<<grid, kTW * 32, p.smem, st>>>(static_cast<__nv_bfloat16*>(out), ldo, q,
+                                       static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc),
+                                       hb, mix, q_cu, kv_cu, bt, cbl, H, G, dim, vdim, bs, scale, cap, size, p.VW,
+                                       p.parts, p.npu, p.nbuf);
+  B200_LAUNCH_OK("sigmoid_attn_prefill_kernel");
+  return B200_OK;
+}
+
 #define SA_DISPATCH(dtype, ...)                                                  \
   switch (dtype) {                                                               \
     case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
@@ -297,6 +575,36 @@ int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cach
   SA_RQ(1);
 #undef SA_RQ
   return B200_OK;
+}
+
+int b200_sigmoid_attn_prefill_supported(int64_t H, int64_t G, int64_t dim, int64_t vdim, int has_mix, int dtype) {
+  if (dtype != B200_BF16 || H <= 0 || G <= 0) return 0;
+  return plan_prefill((int)H, (int)G, (int)dim, (int)vdim, has_mix != 0).ok ? 1 : 0;
+}
+
+int b200_sigmoid_attn_prefill(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
+                              const float* head_bias, const float* head_mix, const int32_t* q_cu_lens,
+                              const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
+                              int64_t n_seq, int64_t q_max, int64_t H, int64_t G, int64_t dim, int64_t vdim,
+                              int64_t block_size, float scale, float cap, int64_t size, int dtype,
+                              b200_stream_t stream) {
+  if (n_seq == 0 || q_max == 0) return B200_OK;
+  B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens,
+                 "sigmoid_attn_prefill: null pointer");
+  B200_CHECK_ARG(dtype == B200_BF16 && n_seq > 0 && q_max > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 &&
+                     ldo >= H * vdim && size >= 0 && size < (1ll << 31) && ldo % 2 == 0,
+                 "sigmoid_attn_prefill: bad shape (bf16 only)");
+  const PrefillPlan p = plan_prefill((int)H, (int)G, (int)dim, (int)vdim, head_mix != nullptr);
+  if (!p.ok) return set_error(B200_ERR_UNSUPPORTED, "sigmoid_attn_prefill: sizes %d x %d / %d heads do not fit",
+                              (int)dim, (int)vdim, (int)H);
+  auto st = static_cast<cudaStream_t>(stream);
+#define SP_ARGS p, out, ldo, q, k_cache, v_cache, head_bias, head_mix, q_cu_lens, kv_cu_lens, block_tables, cu_block_lens, \
+                n_seq, q_max, (int)H, (int)G, (int)dim, (int)vdim, (int)block_size, scale, cap, (int)size, st
+  if (p.upw == 1 && p.npu <= 4) return launch_prefill<1, 4>(SP_ARGS);
+  if (p.upw == 1) return launch_prefill<1, 8>(SP_ARGS);
+  if (p.upw == 2 && p.npu <= 4) return launch_prefill<2, 4>(SP_ARGS);
+  return launch_prefill<4, 2>(SP_ARGS);
+#undef SP_ARGS
 }
 
 }  // extern "C"

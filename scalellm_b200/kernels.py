@@ -1316,14 +1316,20 @@ def sigmoid_attn_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Ten
     return q
 
 
+# a step whose longest portion has at least this many tokens runs the tensor-core kernel (bf16, fitting sizes)
+SIGMOID_ATTN_PREFILL_MIN_ROWS = 4
+
+
 def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, head_bias: Optional[torch.Tensor],
                  head_mix: Optional[torch.Tensor], q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor,
                  cu_block_lens: torch.Tensor, token_seq: torch.Tensor, block_size: int, scale: float, cap: float,
-                 size: int, q_max: int = 1) -> torch.Tensor:
+                 size: int, q_max: int = 1, n_seq: int = 0) -> torch.Tensor:
     """[rows, H * vdim] in the cache's dtype: out_h = sum_j a'_hj v_j over the keys j <= i of row i's block of `size`
     positions (size 0: every j <= i), a_hj = sigmoid(cap tanh(scale q_h . k_j / cap) + head_bias[h]) and
     a'_h = sum_g head_mix[h, g] a_g (head_bias fp32 [H], head_mix fp32 [H, H], either None).  q_max: the step's
-    longest portion (a host number): CTAs take up to 8 consecutive rows and share their key tiles."""
+    longest portion (a host number): CTAs take up to 8 consecutive rows and share their key tiles.  With n_seq (the
+    step's sequence count) a step with prompt portions in bf16 runs on the tensor cores where the sizes allow it; fp32,
+    single tokens and odd sizes run the CUDA-core kernel."""
     _cuda(q, k_cache, v_cache, head_bias, head_mix)
     _f32(q, head_bias, head_mix)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
@@ -1331,7 +1337,16 @@ def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     G, vdim = v_cache.shape[1], v_cache.shape[2]
     assert head_mix is None or head_mix.shape == (H, H)
     out = torch.empty((rows, H * vdim), dtype=k_cache.dtype, device=q.device)
-    check(_lib.load().b200_sigmoid_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(head_bias),
+    lib = _lib.load()
+    if (n_seq > 0 and q_max >= SIGMOID_ATTN_PREFILL_MIN_ROWS and os.environ.get("B200_SIGMOID_ATTN_IMPL") != "simt"
+            and lib.b200_sigmoid_attn_prefill_supported(H, G, dim, vdim, 1 if head_mix is not None else 0,
+                                                        _dt(k_cache))):
+        check(lib.b200_sigmoid_attn_prefill(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(head_bias),
+                                            _p(head_mix), _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens),
+                                            n_seq, q_max, H, G, dim, vdim, block_size, scale, cap, size,
+                                            _dt(k_cache), _stream()))
+        return out
+    check(lib.b200_sigmoid_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(head_bias),
                                         _p(head_mix), _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens),
                                         _p(token_seq), rows, H, G, dim, vdim, block_size, scale, cap, size,
                                         max(1, q_max), _dt(k_cache), _stream()))

@@ -157,6 +157,13 @@ CONFIGS = {
         (left(2, 2, 16, 16, cap=5.0), right(2, 2, 16, 16, taps=1), moe(3, 2, 16, identity=1, shared_ff=16)),
         (left(3, 1, 20, 12, size=64, rot_dims=20, scaling=SCALING), right(2, 1, 12, 20, taps=5), dense(40)),
     ], width=48, side=0, embed_scale=1.0),
+    # head sizes that fit the tensor-core tiles: blocks of positions that are no multiple of a tile, one layer without
+    # a block limit, more heads than warps
+    "tiles": config([
+        (left(8, 2, 32, 32, size=24, rot_dims=16, scaling=SCALING), right(2, 1, 16, 16, taps=4), dense(64)),
+        (left(4, 4, 16, 48, rot_dims=16), right(2, 2, 16, 16, taps=2), moe(4, 2, 16, identity=1)),
+        (left(20, 5, 16, 16, size=50, rot_dims=8, cap=0.0), right(2, 2, 8, 8, taps=3), None),
+    ], width=64, side=4),
     # sizes that are no multiple of four, blocks of one position and of two, many small heads
     "odd": config([
         (left(5, 5, 6, 10, size=1, rot_dims=2), right(5, 5, 10, 6, taps=3), moe(8, 4, 10, identity=4, groups=(3, 1))),
