@@ -747,13 +747,16 @@ B200_API int b200_sigmoid_attn_prepare(float* q_out, const void* q_in, const voi
  * (size 0: all j <= i); a_hj = sigmoid(cap tanh(scale q_h . k_j / cap) + head_bias[h]) (cap 0: no cap), not normalised;
  * a'_hj = sum_g head_mix[h, g] a_gj (head_mix fp32 [H, H], nullable: a' = a).  q fp32 [rows, H, dim]; caches
  * [slots, G, dim] and [slots, G, vdim] of type `dtype`.  rows_per_cta: a hint (the longest portion of the step): CTAs
- * take up to 8 consecutive rows and share the key tiles among them.  CUDA cores, any sizes with H * vdim <= 8192. */
+ * take up to 8 consecutive rows and share the key tiles among them.  n_splits > 1 (single rows only): every row's key
+ * tiles are shared out over that many CTAs whose sums a second kernel adds up through the workspace (fp32, rows *
+ * n_splits * H * vdim floats).  CUDA cores, any sizes with H * vdim <= 8192. */
 B200_API int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cache, const void* v_cache,
                                const float* head_bias /*nullable*/, const float* head_mix /*nullable*/,
                                const int32_t* q_cu_lens, const int32_t* kv_cu_lens, const int32_t* block_tables,
                                const int32_t* cu_block_lens, const int32_t* token_seq, int64_t rows, int64_t H,
                                int64_t G, int64_t dim, int64_t vdim, int64_t block_size, float scale, float cap,
-                               int64_t size, int64_t rows_per_cta, int dtype, b200_stream_t stream);
+                               int64_t size, int64_t rows_per_cta, int64_t n_splits, float* workspace /*nullable*/,
+                               int64_t workspace_floats, int dtype, b200_stream_t stream);
 /* The same for prompt portions in bf16 on the tensor cores: tiles of 16 consecutive tokens of a sequence x all heads
  * (dim and vdim multiples of 16 and shared memory for the heads' queries and one key tile: ..._supported tells);
  * q_max: the longest portion of the step. */

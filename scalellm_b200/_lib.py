@@ -165,7 +165,7 @@ SIGNATURES = {
     "b200_sigmoid_attn_prepare": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                          _i64, _i64, _i64, _i64, _int, _vp]),
     "b200_sigmoid_attn": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
-                                 _i64, _i64, _f32, _f32, _i64, _i64, _int, _vp]),
+                                 _i64, _i64, _f32, _f32, _i64, _i64, _i64, _vp, _i64, _int, _vp]),
     "b200_sigmoid_attn_prefill_supported": (_int, [_i64, _i64, _i64, _i64, _int, _int]),
     "b200_sigmoid_attn_prefill": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64,
                                          _i64, _i64, _i64, _f32, _f32, _i64, _int, _vp]),

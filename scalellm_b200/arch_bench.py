@@ -737,7 +737,7 @@ def fesupel_kernels_alone(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 
         hbias, mix = r32(H) - 3.0, torch.eye(H, device=dev) + 0.1 * r32(H, H)
         f_sig = lambda size: (lambda: kernels.sigmoid_attn(q, kc, vc, hbias, mix, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,
                                                            prm.block_tables, prm.cu_block_lens, prm.token_seq, bs,
-                                                           dim ** -0.5, 30.0, size, q_len))
+                                                           dim ** -0.5, 30.0, size, q_len, batch, ctx))
         kl, vl = rnd(n_blocks * bs, G, dim), rnd(n_blocks * bs, G, dim)
         ql, ol = rnd(rows, H, dim), torch.empty((rows, H, dim), dtype=torch.bfloat16, device=dev)
         f_llama = lambda: kernels.paged_kv_varlen_mha(ol, ql, kl, vl, prm.q_cu_seq_lens, prm.kv_cu_seq_lens,

@@ -217,12 +217,15 @@ gated_delta_prepare_kernel(float* __restrict__ q_out, float* __restrict__ k_out,
                            const int* __restrict__ positions, const int* __restrict__ token_seq,
                            const int* __restrict__ state_slots, int H, int G, int dim, int vdim, int taps,
                            float unit_eps) {
-  const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a row's work is shared out over gridDim.y CTAs (steps of few rows would otherwise leave most SMs idle)
+  const int row = blockIdx.x, lane = threadIdx.x & 31;
+  const int warp = blockIdx.y * (kGdPrepThreads / 32) + (threadIdx.x >> 5), n_warps = gridDim.y * (kGdPrepThreads / 32);
+  const int tid = blockIdx.y * kGdPrepThreads + threadIdx.x, n_thr = gridDim.y * kGdPrepThreads;
   const int seq = token_seq[row], r = row - q_cu[seq], pos = positions[row];
   const int nqk = G * dim, nv = H * vdim, n_ch = 2 * nqk + nv;
   const float* fs = fstate + (size_t)state_slots[seq] * (taps - 1) * n_ch;
   // queries and keys: a warp per head, the head's filtered channels stay in registers for the unit norm
-  for (int u = warp; u < 2 * G; u += kGdPrepThreads / 32) {
+  for (int u = warp; u < 2 * G; u += n_warps) {
     const bool is_q = u < G;
     const int head = is_q ? u : u - G;
     const T* x = is_q ? q_in : k_in;
@@ -248,13 +251,13 @@ gated_delta_prepare_kernel(float* __restrict__ q_out, float* __restrict__ k_out,
       if (t < dim) dst[t] = vals[i] * sc;
     }
   }
-  for (int c = threadIdx.x; c < nv; c += kGdPrepThreads)
+  for (int c = tid; c < nv; c += n_thr)
     v_out[(size_t)row * nv + c] = silu_f(filtered<T>(v_in, ld, wv, fs, n_ch, 2 * nqk + c, row, r, pos, c, taps));
-  for (int c = threadIdx.x; c < H * dim; c += kGdPrepThreads) {
+  for (int c = tid; c < H * dim; c += n_thr) {
     const float sp = softplus_f(Num<T>::to_f(a_in[(size_t)row * ld_a + c]) + dt_bias[c]);
     decay_out[(size_t)row * H * dim + c] = expf(-expf(a_log[c / dim]) * sp);
   }
-  for (int h = threadIdx.x; h < H; h += kGdPrepThreads)
+  for (int h = tid; h < H; h += n_thr)
     beta_out[(size_t)row * H + h] = 1.0f / (1.0f + expf(-Num<T>::to_f(beta_in[(size_t)row * ld + h])));
 }
 
@@ -269,7 +272,7 @@ __global__ void filter_state_carry_kernel(float* __restrict__ fstate, const T* _
   if (n <= 0) return;
   const int n_ch = 2 * nqk + nv;
   float* fs = fstate + (size_t)state_slots[seq] * (taps - 1) * n_ch;
-  for (int c = threadIdx.x; c < n_ch; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n_ch; c += gridDim.y * blockDim.x) {
     const T* x = c < nqk ? q_in + c : (c < 2 * nqk ? k_in + (c - nqk) : v_in + (c - 2 * nqk));
     for (int i = 0; i < taps - 1; ++i) {            // ascending: entry i reads entry i + n > i of the old state
       const int r = n - (taps - 1) + i;
@@ -415,14 +418,20 @@ int b200_gated_delta_prepare(float* q_out, float* k_out, float* v_out, float* de
                  "gated_delta_prepare: bad shape (key size <= 256, taps <= 16, heads a multiple of query/key heads)");
   auto st = static_cast<cudaStream_t>(stream);
   GD_DISPATCH(dtype, {
-    gated_delta_prepare_kernel<T><<<(unsigned)rows, kGdPrepThreads, 0, st>>>(
+    // few rows: up to 8 CTAs per row, so that a step of single tokens still fills the SMs
+    const int work = (int)((2 * G * dim + H * vdim + H * dim + kGdPrepThreads * 4 - 1) / (kGdPrepThreads * 4));
+    int split = (int)((2 * sm_count() + rows - 1) / rows);
+    split = split < 1 ? 1 : (split > 8 ? 8 : split);
+    if (split > work) split = work < 1 ? 1 : work;
+    gated_delta_prepare_kernel<T><<<dim3((unsigned)rows, (unsigned)split), kGdPrepThreads, 0, st>>>(
         q_out, k_out, v_out, decay_out, beta_out, static_cast<const T*>(q_in), static_cast<const T*>(k_in),
         static_cast<const T*>(v_in), static_cast<const T*>(beta_in), ld, static_cast<const T*>(decay_in), ld_decay,
         q_filter, k_filter, v_filter, a_log, dt_bias, filter_state, q_cu_lens, positions, token_seq, state_slots,
         (int)H, (int)G, (int)dim, (int)vdim, (int)taps, unit_eps);
     B200_LAUNCH_OK("gated_delta_prepare_kernel");
     if (taps > 1) {
-      filter_state_carry_kernel<T><<<(unsigned)n_seq, 256, 0, st>>>(
+      const int csplit = (int)((2 * G * dim + H * vdim + 1023) / 1024);
+      filter_state_carry_kernel<T><<<dim3((unsigned)n_seq, (unsigned)(csplit > 8 ? 8 : csplit)), 256, 0, st>>>(
           filter_state, static_cast<const T*>(q_in), static_cast<const T*>(k_in), static_cast<const T*>(v_in), ld,
           q_cu_lens, state_slots, (int)(G * dim), (int)(H * vdim), (int)taps);
       B200_LAUNCH_OK("filter_state_carry_kernel");

@@ -81,7 +81,9 @@ sigmoid_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ 
                     const float* __restrict__ head_mix, const int* __restrict__ q_cu, const int* __restrict__ kv_cu,
                     const int* __restrict__ block_tables, const int* __restrict__ cu_block_lens,
                     const int* __restrict__ token_seq, int rows, int H, int G, int dim, int vdim, int block_size,
-                    float scale, float cap, int size) {
+                    float scale, float cap, int size, float* __restrict__ partial) {
+  // gridDim.y > 1: CTA (b, s) takes every gridDim.y-th key tile of its rows and leaves its sums in
+  // partial[row][s][H * vdim] (the weights are not normalised over the keys, so the shares simply add up)
   extern __shared__ __align__(16) float sm[];
   float* q_s = sm;                                   // [RQ][H][dim]
   float* a_s = q_s + (size_t)RQ * H * dim;           // [RQ][H][KT]  raw weights
@@ -117,7 +119,7 @@ sigmoid_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ 
 #pragma unroll
       for (int c = 0; c < NC; ++c) acc[r][c] = 0.0f;
 
-    for (int t0 = j0; t0 <= p_last; t0 += KT) {
+    for (int t0 = j0 + (int)blockIdx.y * KT; t0 <= p_last; t0 += KT * (int)gridDim.y) {
       const int nk = min(KT, p_last + 1 - t0);
       __syncthreads();                                                     // tile before consumed; q_s visible
       if (threadIdx.x < KT) {
@@ -185,7 +187,10 @@ sigmoid_attn_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ 
       if (o < nout) {
 #pragma unroll
         for (int r = 0; r < RQ; ++r)
-          if (r < n) out[(size_t)(run0 + r) * ldo + o] = Num<T>::from_f(acc[r][c]);
+          if (r < n) {
+            if (partial) partial[((size_t)(run0 + r) * gridDim.y + blockIdx.y) * nout + o] = acc[r][c];
+            else out[(size_t)(run0 + r) * ldo + o] = Num<T>::from_f(acc[r][c]);
+          }
       }
     }
     run0 += n;
@@ -470,6 +475,17 @@ int launch_prefill(const PrefillPlan& p, void* out, int64_t ldo, const float* q,
   return B200_OK;
 }
 
+template <typename T>
+__global__ void sigmoid_attn_sum_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ partial, int nout,
+                                        int n_splits) {
+  const int row = blockIdx.x;
+  for (int o = threadIdx.x; o < nout; o += blockDim.x) {
+    float acc = 0.0f;
+    for (int s = 0; s < n_splits; ++s) acc += partial[((size_t)row * n_splits + s) * nout + o];
+    out[(size_t)row * ldo + o] = Num<T>::from_f(acc);
+  }
+}
+
 #define SA_DISPATCH(dtype, ...)                                                  \
   switch (dtype) {                                                               \
     case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
@@ -482,7 +498,7 @@ template <typename T, int NC, int RQ>
 int launch_attn(void* out, int64_t ldo, const float* q, const void* kc, const void* vc, const float* hb,
                 const float* mix, const int* q_cu, const int* kv_cu, const int* bt, const int* cbl, const int* ts,
                 int64_t rows, int H, int G, int dim, int vdim, int bs, float scale, float cap, int size,
-                cudaStream_t st) {
+                int n_splits, float* partial, cudaStream_t st) {
   if constexpr (NC * RQ > 32) {
     return set_error(B200_ERR_UNSUPPORTED, "sigmoid_attn: %d sums per thread", NC * RQ);
   } else {
@@ -491,11 +507,15 @@ int launch_attn(void* out, int64_t ldo, const float* q, const void* kc, const vo
   auto kern = sigmoid_attn_kernel<T, NC, RQ>;
   if (smem > 48 * 1024)
     B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const unsigned grid = (unsigned)((rows + RQ - 1) / RQ);
+  const dim3 grid((unsigned)((rows + RQ - 1) / RQ), (unsigned)n_splits);
   kern<<<grid, kAttnThreads, smem, st>>>(static_cast<T*>(out), ldo, q, static_cast<const T*>(kc),
                                          static_cast<const T*>(vc), hb, mix, q_cu, kv_cu, bt, cbl, ts, (int)rows, H,
-                                         G, dim, vdim, bs, scale, cap, size);
+                                         G, dim, vdim, bs, scale, cap, size, n_splits > 1 ? partial : nullptr);
   B200_LAUNCH_OK("sigmoid_attn_kernel");
+  if (n_splits > 1) {
+    sigmoid_attn_sum_kernel<T><<<(unsigned)rows, 256, 0, st>>>(static_cast<T*>(out), ldo, partial, H * vdim, n_splits);
+    B200_LAUNCH_OK("sigmoid_attn_sum_kernel");
+  }
   return B200_OK;
   }
 }
@@ -504,10 +524,10 @@ template <typename T, int RQ>
 int launch_attn_nc(int nc, void* out, int64_t ldo, const float* q, const void* kc, const void* vc, const float* hb,
                    const float* mix, const int* q_cu, const int* kv_cu, const int* bt, const int* cbl, const int* ts,
                    int64_t rows, int H, int G, int dim, int vdim, int bs, float scale, float cap, int size,
-                   cudaStream_t st) {
+                   int n_splits, float* partial, cudaStream_t st) {
 #define SA_NC(N)                                                                                                  \
   return launch_attn<T, N, RQ>(out, ldo, q, kc, vc, hb, mix, q_cu, kv_cu, bt, cbl, ts, rows, H, G, dim, vdim, bs, \
-                               scale, cap, size, st)
+                               scale, cap, size, n_splits, partial, st)
   if (nc <= 1) SA_NC(1);
   if (nc <= 2) SA_NC(2);
   if (nc <= 4) SA_NC(4);
@@ -550,8 +570,8 @@ int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cach
                       const float* head_bias, const float* head_mix, const int32_t* q_cu_lens,
                       const int32_t* kv_cu_lens, const int32_t* block_tables, const int32_t* cu_block_lens,
                       const int32_t* token_seq, int64_t rows, int64_t H, int64_t G, int64_t dim, int64_t vdim,
-                      int64_t block_size, float scale, float cap, int64_t size, int64_t rows_per_cta, int dtype,
-                      b200_stream_t stream) {
+                      int64_t block_size, float scale, float cap, int64_t size, int64_t rows_per_cta,
+                      int64_t n_splits, float* workspace, int64_t workspace_floats, int dtype, b200_stream_t stream) {
   if (rows == 0) return B200_OK;
   B200_CHECK_ARG(out && q && k_cache && v_cache && q_cu_lens && kv_cu_lens && block_tables && cu_block_lens &&
                      token_seq,
@@ -564,11 +584,14 @@ int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cach
   // rows per CTA: consecutive rows of a sequence share the key tiles they read; registers hold rows x nc sums
   int rq = rows_per_cta >= 8 ? 8 : (rows_per_cta >= 4 ? 4 : 1);
   while (rq > 1 && (rq * nc > 32 || (size_t)rq * H * (dim + 2 * KT) * 4 > 160 * 1024)) rq /= 2;
+  if (n_splits < 1 || rq > 1) n_splits = 1;       // key tiles are shared out over CTAs for single rows only
+  B200_CHECK_ARG(n_splits == 1 || (workspace && workspace_floats >= rows * n_splits * H * vdim && n_splits <= 65535),
+                 "sigmoid_attn: the workspace takes rows * n_splits * H * vdim floats");
 #define SA_RQ(N)                                                                                                     \
   SA_DISPATCH(dtype, return (launch_attn_nc<T, N>(nc, out, ldo, q, k_cache, v_cache, head_bias, head_mix, q_cu_lens, \
                                                   kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H,  \
                                                   (int)G, (int)dim, (int)vdim, (int)block_size, scale, cap,          \
-                                                  (int)size, st)))
+                                                  (int)size, (int)n_splits, workspace, st)))
   if (rq >= 8) { SA_RQ(8); }
   if (rq >= 4) { SA_RQ(4); }
   if (rq >= 2) { SA_RQ(2); }

@@ -1323,13 +1323,15 @@ SIGMOID_ATTN_PREFILL_MIN_ROWS = 4
 def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, head_bias: Optional[torch.Tensor],
                  head_mix: Optional[torch.Tensor], q_cu: torch.Tensor, kv_cu: torch.Tensor, block_tables: torch.Tensor,
                  cu_block_lens: torch.Tensor, token_seq: torch.Tensor, block_size: int, scale: float, cap: float,
-                 size: int, q_max: int = 1, n_seq: int = 0) -> torch.Tensor:
+                 size: int, q_max: int = 1, n_seq: int = 0, kv_max: int = 0, n_splits: int = 0) -> torch.Tensor:
     """[rows, H * vdim] in the cache's dtype: out_h = sum_j a'_hj v_j over the keys j <= i of row i's block of `size`
     positions (size 0: every j <= i), a_hj = sigmoid(cap tanh(scale q_h . k_j / cap) + head_bias[h]) and
     a'_h = sum_g head_mix[h, g] a_g (head_bias fp32 [H], head_mix fp32 [H, H], either None).  q_max: the step's
     longest portion (a host number): CTAs take up to 8 consecutive rows and share their key tiles.  With n_seq (the
     step's sequence count) a step with prompt portions in bf16 runs on the tensor cores where the sizes allow it; fp32,
-    single tokens and odd sizes run the CUDA-core kernel."""
+    single tokens and odd sizes run the CUDA-core kernel.  A step of single tokens with fewer rows than two CTAs per SM
+    shares every row's key tiles out over several CTAs (kv_max: an upper bound of the cached lengths, sizes the split;
+    n_splits forces it)."""
     _cuda(q, k_cache, v_cache, head_bias, head_mix)
     _f32(q, head_bias, head_mix)
     _check_i32(q_cu, kv_cu, block_tables, cu_block_lens, token_seq)
@@ -1346,10 +1348,21 @@ def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                                             n_seq, q_max, H, G, dim, vdim, block_size, scale, cap, size,
                                             _dt(k_cache), _stream()))
         return out
+    ws = None
+    if q_max <= 1:
+        if n_splits <= 0:
+            visible = min(kv_max, size) if size > 0 else kv_max
+            tiles = max(1, -(-visible // 32))
+            n_splits = max(1, min(296 // max(rows, 1), tiles // 2, 64))
+        if n_splits > 1:
+            ws = torch.empty(rows * n_splits * H * vdim, dtype=torch.float32, device=q.device)
+    else:
+        n_splits = 1
     check(lib.b200_sigmoid_attn(_p(out), H * vdim, _p(q), _p(k_cache), _p(v_cache), _p(head_bias),
-                                        _p(head_mix), _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens),
-                                        _p(token_seq), rows, H, G, dim, vdim, block_size, scale, cap, size,
-                                        max(1, q_max), _dt(k_cache), _stream()))
+                                _p(head_mix), _p(q_cu), _p(kv_cu), _p(block_tables), _p(cu_block_lens),
+                                _p(token_seq), rows, H, G, dim, vdim, block_size, scale, cap, size,
+                                max(1, q_max), n_splits, _p(ws), ws.numel() if ws is not None else 0, _dt(k_cache),
+                                _stream()))
     return out
 
 

@@ -1091,7 +1091,7 @@ class SigmoidBlockAttention:
         o = kernels.sigmoid_attn(q, cache.key_cache, cache.value_cache, self.head_bias, self.head_mix,
                                  params.q_cu_seq_lens, params.kv_cu_seq_lens, params.block_tables,
                                  params.cu_block_lens, params.token_seq, cache.block_size(), self.scale, self.cap,
-                                 self.size, params.q_max_seq_len, params.num_sequences)
+                                 self.size, params.q_max_seq_len, params.num_sequences, params.kv_max_seq_len)
         return self.o_proj(o)
 
     def forward(self, h: torch.Tensor, positions: torch.Tensor, cache: KVCache, params: InputParameters) -> torch.Tensor:

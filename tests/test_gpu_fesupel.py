@@ -234,7 +234,8 @@ def test_attention_inputs_bias_turn_and_cache_rows(dtype, H, G, dim, vdim, rot):
     assert bool((kc.cpu()[mask] == 7.0).all()) and bool((vc.cpu()[mask] == 7.0).all())
 
 
-def _attend_case(dtype, H, G, dim, vdim, size, block_size, cached, n_new, loud, seed=0, mix=True, cap=0.0, simt=False):
+def _attend_case(dtype, H, G, dim, vdim, size, block_size, cached, n_new, loud, seed=0, mix=True, cap=0.0, simt=False,
+                 n_splits=0):
     """A hand-made cache of one sequence: every key is quiet (its weight is sigmoid of a very negative number) but
     the one at position `loud`, whose weight is close to one for head 0 of every group: a row that sees it carries
     its value, a row that does not carries almost nothing."""
@@ -258,7 +259,7 @@ def _attend_case(dtype, H, G, dim, vdim, size, block_size, cached, n_new, loud, 
     kc[sl], vc[sl] = K.to(DEV), V.to(DEV)
     got = kernels.sigmoid_attn(q.to(DEV), kc, vc, hb_.to(DEV), None if T is None else T.to(DEV), par.q_cu_seq_lens,
                                par.kv_cu_seq_lens, par.block_tables, par.cu_block_lens, par.token_seq, block_size,
-                               1.0, cap, size, n_new, 0 if simt else 1)
+                               1.0, cap, size, n_new, 0 if simt else 1, n, n_splits)
     positions = torch.arange(cached, n)
     want = of.sigmoid_attend(q.double(), K.double(), V.double(), positions, 1.0, cap, hb_.double(),
                              None if T is None else T.double(), size)
@@ -280,6 +281,9 @@ def test_attention_block_edges_in_prompts_and_decoding(dtype, H, G, dim, vdim):
         got, want, V = _attend_case(dtype, H, G, dim, vdim, size, 4, cached, n_new, loud, seed=cached)
         close(got, want, dtype, f"size {size} cached {cached} loud {loud}")
         assert (float(want.abs().max()) > 0.3) == seen
+        for n_splits in (1, 2, 3, 9):          # the row's key tiles shared out over several CTAs
+            got, _, _ = _attend_case(dtype, H, G, dim, vdim, size, 4, cached, n_new, loud, seed=cached, n_splits=n_splits)
+            close(got, want, dtype, f"size {size} cached {cached} loud {loud}, {n_splits} shares")
     # portions: rows on both sides of an edge in one step, with the loud key on either side of it
     for size, cached, n_new, loud in ((10, 14, 13, 19), (10, 14, 13, 20), (7, 0, 40, 6), (7, 0, 40, 7), (0, 100, 70, 3),
                                       (33, 60, 10, 65), (1, 5, 9, 8)):
