@@ -486,6 +486,251 @@ __global__ void sigmoid_attn_sum_kernel(T* __restrict__ out, int64_t ldo, const 
   }
 }
 
+
+// Single rows (decoding) with vector loads: one CTA per (row, share of the row's key tiles).
+//   scores : 16 lanes per (key, key/value head): one 16-byte load a lane, the dot products with the group's R query
+//            heads, a butterfly over the 16 lanes
+//   mix    : thread = (head, key), as above
+//   sum    : thread = (key/value head, 16 bytes of value channels, one of KG key groups): R x EPV sums in registers;
+//            the KG groups are added up through shared memory at the end
+// dim and vdim multiples of EPV = 16 / sizeof(T), at most 256 (head, chunk) items, R <= RMAX.
+template <typename T, int RMAX>
+__global__ void __launch_bounds__(kAttnThreads)
+sigmoid_attn_decode_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q,
+                           const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                           const float* __restrict__ head_bias, const float* __restrict__ head_mix,
+                           const int* __restrict__ q_cu, const int* __restrict__ kv_cu,
+                           const int* __restrict__ block_tables, const int* __restrict__ cu_block_lens,
+                           const int* __restrict__ token_seq, int H, int G, int dim, int vdim, int block_size,
+                           float scale, float cap, int size, float* __restrict__ partial) {
+  constexpr int EPV = 16 / (int)sizeof(T);
+  extern __shared__ __align__(16) float sm[];
+  const int R = H / G;
+  const int NI = G * (vdim / EPV);                       // (key/value head, chunk) items of the sum
+  const int KG = kAttnThreads / NI;                      // key groups
+  const int QROW = dim + (dim / 32) * 4;                 // four floats of padding per 32: the 16 lanes' 16-byte reads
+                                                         // of one head fall on distinct banks
+  float* q_s = sm;                                       // [H][QROW]
+  float* a_s = q_s + (size_t)H * QROW;                   // [H][KT]
+  float* m_s = a_s + (size_t)H * KT;                     // [H][KT]
+  float* mix_s = m_s + (size_t)H * KT;                   // [H][H]
+  float* hb_s = mix_s + (head_mix ? H * H : 0);          // [H]
+  float* red_s = hb_s + H;                               // [KG][NI][R][EPV]
+  __shared__ int slot_s[KT];
+  const int row = blockIdx.x;
+  const int seq = token_seq[row];
+  const int kv_len = kv_cu[seq + 1] - kv_cu[seq], q_len = q_cu[seq + 1] - q_cu[seq];
+  const int p = kv_len - q_len + (row - q_cu[seq]);      // position of the row
+  const int j0 = size > 0 ? (p / size) * size : 0;
+  const int* table = block_tables + cu_block_lens[seq];
+  const size_t k_stride = (size_t)G * dim, v_stride = (size_t)G * vdim;
+  if (head_mix)
+    for (int i = threadIdx.x; i < H * H; i += kAttnThreads) mix_s[i] = head_mix[i];
+  for (int i = threadIdx.x; i < H; i += kAttnThreads) hb_s[i] = head_bias ? head_bias[i] : 0.0f;
+  for (int i = threadIdx.x; i < H * dim; i += kAttnThreads) {
+    const int h = i / dim, d = i - h * dim;
+    q_s[h * QROW + d + (d / 32) * 4] = q[(size_t)row * H * dim + i];
+  }
+  const int item = threadIdx.x % NI, kq = threadIdx.x / NI;     // kq >= KG: the thread has no part in the sum
+  const int ig = item / (vdim / EPV), ich = item % (vdim / EPV);
+  float acc[RMAX][EPV];
+#pragma unroll
+  for (int r = 0; r < RMAX; ++r)
+#pragma unroll
+    for (int e = 0; e < EPV; ++e) acc[r][e] = 0.0f;
+  const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15;        // 16-lane group and lane within it
+  for (int t0 = j0 + (int)blockIdx.y * KT; t0 <= p; t0 += KT * (int)gridDim.y) {
+    const int nk = min(KT, p + 1 - t0);
+    __syncthreads();                                             // tile before consumed; q_s visible
+    if (threadIdx.x < KT) {
+      const int j = t0 + min((int)threadIdx.x, nk - 1);
+      slot_s[threadIdx.x] = table[j / block_size] + j % block_size;
+    }
+    __syncthreads();
+    // both 16-lane groups of a warp make the same number of rounds (the butterflies take the whole warp); a round
+    // takes UB units a group, all their loads issued before the first product, so that a CTA has several loads in
+    // flight per thread (the walk is bound by the latency of its loads, not by their number)
+    constexpr int UB = 4;
+    for (int ub = hw & ~1; ub < nk * G; ub += UB * (kAttnThreads / 16)) {
+      bool ok[UB];
+      int jj[UB], g[UB];
+      float part[UB][RMAX];
+#pragma unroll
+      for (int i = 0; i < UB; ++i) {
+        const int u = ub + i * (kAttnThreads / 16) + (hw & 1);
+        ok[i] = u < nk * G;
+        const int uu = ok[i] ? u : 0;
+        jj[i] = uu / G;
+        g[i] = uu - jj[i] * G;
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) part[i][r] = 0.0f;
+      }
+      for (int d = hl * EPV; d < dim; d += 16 * EPV) {
+        uint4 raw[UB];
+#pragma unroll
+        for (int i = 0; i < UB; ++i)
+          raw[i] = ok[i] ? ld_nc_v4(k_cache + (size_t)slot_s[jj[i]] * k_stride + (size_t)g[i] * dim + d)
+                         : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < UB; ++i) {
+          float kv[EPV];
+          if constexpr (sizeof(T) == 4) {
+            kv[0] = __uint_as_float(raw[i].x); kv[1] = __uint_as_float(raw[i].y);
+            kv[2] = __uint_as_float(raw[i].z); kv[3] = __uint_as_float(raw[i].w);
+          } else {
+            const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const float2 f = Num<T>::unpack(w4[c]);
+              kv[2 * c] = f.x;
+              kv[2 * c + 1] = f.y;
+            }
+          }
+#pragma unroll
+          for (int r = 0; r < RMAX; ++r)
+            if (r < R) {
+              const float* qh = q_s + (size_t)(g[i] * R + r) * QROW + d + (d / 32) * 4;
+#pragma unroll
+              for (int e = 0; e < EPV; e += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qh + e);
+                part[i][r] += q4.x * kv[e] + q4.y * kv[e + 1] + q4.z * kv[e + 2] + q4.w * kv[e + 3];
+              }
+            }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < UB; ++i)
+#pragma unroll
+        for (int r = 0; r < RMAX; ++r) {
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) part[i][r] += __shfl_xor_sync(0xffffffffu, part[i][r], o);
+          if (ok[i] && r < R && hl == 0) a_s[(g[i] * R + r) * KT + jj[i]] = part[i][r];     // the raw product
+        }
+    }
+    __syncthreads();
+    // cap, bias and sigmoid with every lane at work (one lane per product would leave 15 of 16 idle)
+    for (int i = threadIdx.x; i < H * KT; i += kAttnThreads) {
+      const int h = i / KT;
+      float w = 0.0f;
+      if (i - h * KT < nk) {
+        float sc = a_s[i] * scale;
+        if (cap > 0.0f) sc = cap * tanhf(sc / cap);
+        w = sigmoidf_(sc + hb_s[h]);
+      }
+      a_s[i] = w;
+    }
+    __syncthreads();
+    const float* w_s = a_s;
+    if (head_mix) {
+      for (int i = threadIdx.x; i < H * KT; i += kAttnThreads) {
+        const int jj = i % KT, h = i / KT;
+        float m = 0.0f;
+        for (int g2 = 0; g2 < H; ++g2) m += mix_s[h * H + g2] * a_s[g2 * KT + jj];
+        m_s[i] = m;
+      }
+      __syncthreads();
+      w_s = m_s;
+    }
+    if (kq < KG) {
+      const T* vb = v_cache + (size_t)ig * vdim + (size_t)ich * EPV;
+      for (int jb = kq; jb < nk; jb += UB * KG) {          // UB keys a round, loads first
+        uint4 raw[UB];
+#pragma unroll
+        for (int i = 0; i < UB; ++i) {
+          const int jj = jb + i * KG;
+          raw[i] = jj < nk ? ld_nc_v4(vb + (size_t)slot_s[jj] * v_stride) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int i = 0; i < UB; ++i) {
+          const int jj = jb + i * KG;
+          if (jj < nk) {
+            float vv[EPV];
+            if constexpr (sizeof(T) == 4) {
+              vv[0] = __uint_as_float(raw[i].x); vv[1] = __uint_as_float(raw[i].y);
+              vv[2] = __uint_as_float(raw[i].z); vv[3] = __uint_as_float(raw[i].w);
+            } else {
+              const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const float2 f = Num<T>::unpack(w4[c]);
+                vv[2 * c] = f.x;
+                vv[2 * c + 1] = f.y;
+              }
+            }
+#pragma unroll
+            for (int r = 0; r < RMAX; ++r)
+              if (r < R) {
+                const float w = w_s[(ig * R + r) * KT + jj];
+#pragma unroll
+                for (int e = 0; e < EPV; ++e) acc[r][e] += w * vv[e];
+              }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (kq < KG) {
+#pragma unroll
+    for (int r = 0; r < RMAX; ++r)
+      if (r < R) {
+#pragma unroll
+        for (int e = 0; e < EPV; ++e) red_s[(((size_t)kq * NI + item) * R + r) * EPV + e] = acc[r][e];
+      }
+  }
+  __syncthreads();
+  const int nout = H * vdim;
+  for (int o = threadIdx.x; o < nout; o += kAttnThreads) {
+    const int h = o / vdim, c = o - h * vdim;
+    const int g = h / R, r = h - g * R, it = g * (vdim / EPV) + c / EPV, e = c % EPV;
+    float sum = 0.0f;
+    for (int k2 = 0; k2 < KG; ++k2) sum += red_s[(((size_t)k2 * NI + it) * R + r) * EPV + e];
+    if (partial) partial[((size_t)row * gridDim.y + blockIdx.y) * nout + o] = sum;
+    else out[(size_t)row * ldo + o] = Num<T>::from_f(sum);
+  }
+}
+
+template <typename T>
+bool decode_vec_ok(int H, int G, int dim, int vdim, const void* kc, const void* vc) {
+  constexpr int EPV = 16 / (int)sizeof(T);
+  const int R = H / G;
+  return dim % EPV == 0 && vdim % EPV == 0 && G * (vdim / EPV) <= kAttnThreads && R <= 8 && is_aligned(kc, 16) &&
+         is_aligned(vc, 16);
+}
+
+template <typename T>
+int launch_decode_vec(void* out, int64_t ldo, const float* q, const void* kc, const void* vc, const float* hb,
+                      const float* mix, const int* q_cu, const int* kv_cu, const int* bt, const int* cbl, const int* ts,
+                      int64_t rows, int H, int G, int dim, int vdim, int bs, float scale, float cap, int size,
+                      int n_splits, float* partial, cudaStream_t st) {
+  constexpr int EPV = 16 / (int)sizeof(T);
+  const int R = H / G, NI = G * (vdim / EPV), KG = kAttnThreads / NI;
+  const size_t smem = ((size_t)H * (dim + (dim / 32) * 4) + 2 * (size_t)H * KT + (mix ? (size_t)H * H : 0) + H +
+                       (size_t)KG * NI * R * EPV) * sizeof(float);
+  if (smem > 200 * 1024) return set_error(B200_ERR_UNSUPPORTED, "sigmoid_attn: %zu bytes of shared memory", smem);
+  const dim3 grid((unsigned)rows, (unsigned)n_splits);
+#define SD_LAUNCH(RM)                                                                                               \
+  do {                                                                                                              \
+    auto kern = sigmoid_attn_decode_kernel<T, RM>;                                                                  \
+    if (smem > 48 * 1024)                                                                                           \
+      B200_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));             \
+    kern<<<grid, kAttnThreads, smem, st>>>(static_cast<T*>(out), ldo, q, static_cast<const T*>(kc),                 \
+                                           static_cast<const T*>(vc), hb, mix, q_cu, kv_cu, bt, cbl, ts, H, G, dim, \
+                                           vdim, bs, scale, cap, size, n_splits > 1 ? partial : nullptr);           \
+  } while (0)
+  if (R <= 1) SD_LAUNCH(1);
+  else if (R <= 2) SD_LAUNCH(2);
+  else if (R <= 4) SD_LAUNCH(4);
+  else SD_LAUNCH(8);
+#undef SD_LAUNCH
+  B200_LAUNCH_OK("sigmoid_attn_decode_kernel");
+  if (n_splits > 1) {
+    sigmoid_attn_sum_kernel<T><<<(unsigned)rows, 256, 0, st>>>(static_cast<T*>(out), ldo, partial, H * vdim, n_splits);
+    B200_LAUNCH_OK("sigmoid_attn_sum_kernel");
+  }
+  return B200_OK;
+}
+
 #define SA_DISPATCH(dtype, ...)                                                  \
   switch (dtype) {                                                               \
     case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
@@ -587,6 +832,14 @@ int b200_sigmoid_attn(void* out, int64_t ldo, const float* q, const void* k_cach
   if (n_splits < 1 || rq > 1) n_splits = 1;       // key tiles are shared out over CTAs for single rows only
   B200_CHECK_ARG(n_splits == 1 || (workspace && workspace_floats >= rows * n_splits * H * vdim && n_splits <= 65535),
                  "sigmoid_attn: the workspace takes rows * n_splits * H * vdim floats");
+  if (rq == 1) {
+    SA_DISPATCH(dtype, {
+      if (decode_vec_ok<T>((int)H, (int)G, (int)dim, (int)vdim, k_cache, v_cache))
+        return launch_decode_vec<T>(out, ldo, q, k_cache, v_cache, head_bias, head_mix, q_cu_lens, kv_cu_lens,
+                                    block_tables, cu_block_lens, token_seq, rows, (int)H, (int)G, (int)dim, (int)vdim,
+                                    (int)block_size, scale, cap, (int)size, (int)n_splits, workspace, st);
+    });
+  }
 #define SA_RQ(N)                                                                                                     \
   SA_DISPATCH(dtype, return (launch_attn_nc<T, N>(nc, out, ldo, q, k_cache, v_cache, head_bias, head_mix, q_cu_lens, \
                                                   kv_cu_lens, block_tables, cu_block_lens, token_seq, rows, (int)H,  \

@@ -1353,7 +1353,8 @@ def sigmoid_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         if n_splits <= 0:
             visible = min(kv_max, size) if size > 0 else kv_max
             tiles = max(1, -(-visible // 32))
-            n_splits = max(1, min(296 // max(rows, 1), tiles // 2, 64))
+            # about two CTAs per SM (measured: more and shorter walks cost more in their fixed parts than they hide)
+            n_splits = max(1, min(296 // max(rows, 1), tiles, 64))
         if n_splits > 1:
             ws = torch.empty(rows * n_splits * H * vdim, dtype=torch.float32, device=q.device)
     else:
