@@ -786,7 +786,7 @@ B200_API int b200_gated_delta_prepare(float* q_out, float* k_out, float* v_out, 
 /* Per (sequence, head), over the sequence's rows in order, S [dim, vdim] fp32 in state[slot, h] (zero where the
  * portion starts at position 0):  S <- diag(decay) S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q ;
  * out[row, h] = o / rms(o) * norm_weight[vdim] * sigmoid(gate_logits[row, h]).  Head h reads q / k head h / (H / G).
- * dim <= 128, vdim <= 256. */
+ * dim <= 128 with vdim <= 256, or dim <= 256 with vdim <= 128. */
 B200_API int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k, const float* v,
                                    const float* decay, const float* beta, const void* gate_logits, int64_t ld_gate,
                                    const float* norm_weight, float* state, const int32_t* q_cu_lens,

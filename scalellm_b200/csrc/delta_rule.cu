@@ -281,27 +281,34 @@ __global__ void filter_state_carry_kernel(float* __restrict__ fstate, const T* _
   }
 }
 
-template <typename T, int DK, int NT>
+// KS threads share a column of S: thread (column c, part) keeps the DK / KS key rows [part * DK / KS, ...) of the
+// column, and the two sums over the key dimension end in a butterfly over the KS neighbouring lanes.  KS = 1 is the
+// form for key sizes up to 128 (at 128 x 128 two threads per column measured 1.3x slower: the spills and the wider
+// barriers cost more than the shorter serial work saves); KS = 2 carries key sizes up to 256, whose columns do not
+// fit one thread's registers.
+template <typename T, int DK, int NT, int KS>
 __global__ void __launch_bounds__(NT)
 gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ q, const float* __restrict__ k,
                         const float* __restrict__ v, const float* __restrict__ decay, const float* __restrict__ beta,
                         const T* __restrict__ gate, int64_t ld_gate, const float* __restrict__ nw,
                         float* __restrict__ state, const int* __restrict__ q_cu, const int* __restrict__ positions,
                         const int* __restrict__ state_slots, int H, int G, int dim, int vdim, float eps) {
+  constexpr int DL = DK / KS;                       // key rows a thread keeps
   __shared__ __align__(16) float q_s[2][DK], k_s[2][DK], w_s[2][DK];
   __shared__ float red[32];
-  const int seq = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int j = tid / KS, part = tid % KS, k0 = part * DL;
   const int t0 = q_cu[seq], t1 = q_cu[seq + 1];
   if (t0 >= t1) return;
   const int g = h / (H / G);
   const bool live = j < vdim;
   const int nqk = G * dim, nv = H * vdim, nd = H * dim;
   float* Sg = state + (((size_t)state_slots[seq] * H + h) * dim) * vdim;   // [key][value]
-  float S[DK];
+  float S[DL];
   const bool fresh = positions[t0] == 0;
 #pragma unroll
-  for (int kk = 0; kk < DK; ++kk) S[kk] = (live && kk < dim && !fresh) ? Sg[(size_t)kk * vdim + j] : 0.0f;
-  for (int kk = j; kk < DK; kk += NT)
+  for (int kk = 0; kk < DL; ++kk) S[kk] = (live && k0 + kk < dim && !fresh) ? Sg[(size_t)(k0 + kk) * vdim + j] : 0.0f;
+  for (int kk = tid; kk < DK; kk += NT)
     if (kk >= dim) q_s[0][kk] = q_s[1][kk] = k_s[0][kk] = k_s[1][kk] = w_s[0][kk] = w_s[1][kk] = 0.0f;
   const float nwj = live ? nw[j] : 0.0f;
   constexpr int PER = (DK + NT - 1) / NT;        // key channels a thread stages per token
@@ -309,7 +316,7 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
   auto load_token = [&](int t) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int kk = j + i * NT;
+      const int kk = tid + i * NT;
       if (kk < dim) {
         nq[i] = q[(size_t)t * nqk + (size_t)g * dim + kk];
         nk[i] = k[(size_t)t * nqk + (size_t)g * dim + kk];
@@ -327,7 +334,7 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
     const int b = (t - t0) & 1;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
-      const int kk = j + i * NT;
+      const int kk = tid + i * NT;
       if (kk < dim) { q_s[b][kk] = nq[i]; k_s[b][kk] = nk[i]; w_s[b][kk] = nd_[i]; }
     }
     const float vj = nvj, bt = nb, gj = ng;
@@ -335,37 +342,44 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
     __syncthreads();
     float ks4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int kk = 0; kk < DK; kk += 4) {
-      const float4 w4 = *reinterpret_cast<const float4*>(&w_s[b][kk]);
-      const float4 k4 = *reinterpret_cast<const float4*>(&k_s[b][kk]);
+    for (int kk = 0; kk < DL; kk += 4) {
+      const float4 w4 = *reinterpret_cast<const float4*>(&w_s[b][k0 + kk]);
+      const float4 k4 = *reinterpret_cast<const float4*>(&k_s[b][k0 + kk]);
       S[kk] *= w4.x;     ks4[0] += k4.x * S[kk];
       S[kk + 1] *= w4.y; ks4[1] += k4.y * S[kk + 1];
       S[kk + 2] *= w4.z; ks4[2] += k4.z * S[kk + 2];
       S[kk + 3] *= w4.w; ks4[3] += k4.w * S[kk + 3];
     }
-    const float u = bt * (vj - ((ks4[0] + ks4[1]) + (ks4[2] + ks4[3])));
+    float kS = (ks4[0] + ks4[1]) + (ks4[2] + ks4[3]);
+#pragma unroll
+    for (int sh = KS / 2; sh > 0; sh >>= 1) kS += __shfl_xor_sync(0xffffffffu, kS, sh);
+    const float u = bt * (vj - kS);
     float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int kk = 0; kk < DK; kk += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(&k_s[b][kk]);
-      const float4 q4 = *reinterpret_cast<const float4*>(&q_s[b][kk]);
+    for (int kk = 0; kk < DL; kk += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(&k_s[b][k0 + kk]);
+      const float4 q4 = *reinterpret_cast<const float4*>(&q_s[b][k0 + kk]);
       S[kk] += k4.x * u;     o4[0] += S[kk] * q4.x;
       S[kk + 1] += k4.y * u; o4[1] += S[kk + 1] * q4.y;
       S[kk + 2] += k4.z * u; o4[2] += S[kk + 2] * q4.z;
       S[kk + 3] += k4.w * u; o4[3] += S[kk + 3] * q4.w;
     }
-    const float o = live ? (o4[0] + o4[1]) + (o4[2] + o4[3]) : 0.0f;
-    const float o2 = block_sum<NT>(o * o, red);   // its barrier also orders this token's reads before the token
-                                                  // after next overwrites the same staging buffer
-    if (live) {
+    float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+    for (int sh = KS / 2; sh > 0; sh >>= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
+    if (!live) o = 0.0f;
+    const float o2 = block_sum<NT>(part == 0 ? o * o : 0.0f, red);   // its barrier also orders this token's reads
+                                                                     // before the token after next overwrites the
+                                                                     // same staging buffer
+    if (live && part == 0) {
       const float gt = 1.0f / (1.0f + expf(-gj));
       out[(size_t)t * ldo + (size_t)h * vdim + j] = Num<T>::from_f(o * rsqrtf(o2 / (float)vdim + eps) * nwj * gt);
     }
   }
   if (live) {
 #pragma unroll
-    for (int kk = 0; kk < DK; ++kk)
-      if (kk < dim) Sg[(size_t)kk * vdim + j] = S[kk];
+    for (int kk = 0; kk < DL; ++kk)
+      if (k0 + kk < dim) Sg[(size_t)(k0 + kk) * vdim + j] = S[kk];
   }
 }
 
@@ -382,14 +396,21 @@ int launch_gd_scan(int nt, dim3 grid, cudaStream_t st, void* out, int64_t ldo, c
                    const float* v, const float* decay, const float* beta, const void* gate, int64_t ld_gate,
                    const float* nw, float* state, const int* q_cu, const int* positions, const int* slots, int H,
                    int G, int dim, int vdim, float eps) {
-#define GD_NT(N)                                                                                                   \
-  gated_delta_scan_kernel<T, DK, N><<<grid, N, 0, st>>>(static_cast<T*>(out), ldo, q, k, v, decay, beta,             \
-                                                        static_cast<const T*>(gate), ld_gate, nw, state, q_cu,      \
-                                                        positions, slots, H, G, dim, vdim, eps)
-  if (nt <= 32) GD_NT(32);
-  else if (nt <= 64) GD_NT(64);
-  else if (nt <= 128) GD_NT(128);
-  else GD_NT(256);
+#define GD_NT(N, KSP)                                                                                              \
+  gated_delta_scan_kernel<T, DK, N, KSP><<<grid, N, 0, st>>>(static_cast<T*>(out), ldo, q, k, v, decay, beta,        \
+                                                             static_cast<const T*>(gate), ld_gate, nw, state, q_cu, \
+                                                             positions, slots, H, G, dim, vdim, eps)
+  if constexpr (DK > 128) {          // two threads per column: value sizes up to 128
+    if (nt <= 32) GD_NT(64, 2);
+    else if (nt <= 64) GD_NT(128, 2);
+    else if (nt <= 128) GD_NT(256, 2);
+    else return set_error(B200_ERR_UNSUPPORTED, "gated_delta_scan: key size above 128 with value size above 128");
+  } else {
+    if (nt <= 32) GD_NT(32, 1);
+    else if (nt <= 64) GD_NT(64, 1);
+    else if (nt <= 128) GD_NT(128, 1);
+    else GD_NT(256, 1);
+  }
 #undef GD_NT
   B200_LAUNCH_OK("gated_delta_scan_kernel");
   return B200_OK;
@@ -462,7 +483,8 @@ int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k
   if (dim <= 32) { GD_CALL(32); }
   else if (dim <= 64) { GD_CALL(64); }
   else if (dim <= 128) { GD_CALL(128); }
-  else return b200::set_error(B200_ERR_UNSUPPORTED, "gated_delta_scan: key size %d > 128", (int)dim);
+  else if (dim <= 256) { GD_CALL(256); }
+  else return b200::set_error(B200_ERR_UNSUPPORTED, "gated_delta_scan: key size %d > 256", (int)dim);
 #undef GD_CALL
   return B200_OK;
 }

@@ -1120,7 +1120,12 @@ class GatedDeltaMixer:
         self.ra, self.rg = w["a1"].shape[0], w["g1"].shape[0]
         self.in_weight = torch.cat([w["q"], w["k"], w["v"], w["b"], w["a1"], w["g1"]], dim=0)
         self.n_in = self.in_weight.shape[0]
-        self.a2, self.g2 = Linear(w["a2"]), Linear(w["g2"])
+        # the second factors of the decay and gate pairs as ONE product: [a1 h | g1 h] times a block-diagonal weight
+        # (the zero blocks add exact zeros), so a step has one small launch instead of two and two copies
+        low2 = torch.zeros((n_heads * dim + self.nv, self.ra + self.rg), dtype=w["a2"].dtype, device=w["a2"].device)
+        low2[: n_heads * dim, : self.ra] = w["a2"]
+        low2[n_heads * dim:, self.ra:] = w["g2"]
+        self.low2 = Linear(low2)
         f = lambda t: t.to(torch.float32).to(device).contiguous()
         self.q_filter, self.k_filter, self.v_filter = f(w["q.conv"]), f(w["k.conv"]), f(w["v.conv"])
         self.taps = self.q_filter.shape[1]
@@ -1134,14 +1139,14 @@ class GatedDeltaMixer:
     def run(self, proj: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:
         """proj [rows, n_in]: this mixer's column block of the input product."""
         o0 = 2 * self.nqk + self.nv
-        a1 = proj[:, o0 + self.H: o0 + self.H + self.ra].contiguous()
-        g1 = proj[:, o0 + self.H + self.ra: o0 + self.H + self.ra + self.rg].contiguous()
+        low = self.low2(proj[:, o0 + self.H: o0 + self.H + self.ra + self.rg])      # [decay logits | gate logits]
+        nd = self.H * self.dim
         q, k, v, decay, beta = kernels.gated_delta_prepare(
             proj[:, : self.nqk], proj[:, self.nqk: 2 * self.nqk], proj[:, 2 * self.nqk: o0], proj[:, o0: o0 + self.H],
-            self.a2(a1), self.q_filter, self.k_filter, self.v_filter, self.a_log, self.dt_bias, self.filter_state,
+            low[:, :nd], self.q_filter, self.k_filter, self.v_filter, self.a_log, self.dt_bias, self.filter_state,
             params.q_cu_seq_lens, positions, params.token_seq, params.state_slots, self.H, self.G, self.dim, self.vd,
             self.unit_eps)
-        o = kernels.gated_delta_scan(q, k, v, decay, beta, self.g2(g1), self.norm_weight, self.state,
+        o = kernels.gated_delta_scan(q, k, v, decay, beta, low[:, nd:], self.norm_weight, self.state,
                                      params.q_cu_seq_lens, positions, params.state_slots, self.eps)
         return self.o_proj(o)
 

@@ -352,7 +352,8 @@ def _delta_oracle(proj, dec, gate, w, H, G, dim, vdim, st, eps):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,dim,vdim,taps", [(4, 2, 16, 8, 4), (2, 2, 24, 32, 3), (3, 1, 8, 40, 2), (5, 5, 10, 6, 1),
-                                                (2, 1, 128, 64, 4), (1, 1, 33, 130, 5), (6, 3, 64, 64, 4)])
+                                                (2, 1, 128, 64, 4), (1, 1, 33, 130, 5), (6, 3, 64, 64, 4),
+                                                (2, 1, 160, 24, 3), (1, 1, 256, 128, 2)])
 def test_gated_delta_rule_filters_and_state_over_portions(dtype, H, G, dim, vdim, taps):
     """Two sequences in two state slots fed in portions of unequal sizes (1, 2, fewer and more than the taps), the
     second slot used before by another sequence: filter inputs and matrices must carry over exactly."""
