@@ -786,12 +786,15 @@ B200_API int b200_gated_delta_prepare(float* q_out, float* k_out, float* v_out, 
 /* Per (sequence, head), over the sequence's rows in order, S [dim, vdim] fp32 in state[slot, h] (zero where the
  * portion starts at position 0):  S <- diag(decay) S ; u = beta (v - S^T k) ; S <- S + k u^T ; o = S^T q ;
  * out[row, h] = o / rms(o) * norm_weight[vdim] * sigmoid(gate_logits[row, h]).  Head h reads q / k head h / (H / G).
- * dim <= 128 with vdim <= 256, or dim <= 256 with vdim <= 128. */
+ * dim <= 128 with vdim <= 256, or dim <= 256 with vdim <= 128.  raw_workspace (nullable; fp32 [rows, H * vdim], rows =
+ * the step's packed rows): the walk stores the plain read-outs there and a second, token-parallel launch applies the
+ * norm and the gate (long portions: one barrier per token instead of two). */
 B200_API int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k, const float* v,
                                    const float* decay, const float* beta, const void* gate_logits, int64_t ld_gate,
                                    const float* norm_weight, float* state, const int32_t* q_cu_lens,
                                    const int32_t* positions, const int32_t* state_slots, int64_t n_seq, int64_t H,
-                                   int64_t G, int64_t dim, int64_t vdim, float eps, int dtype, b200_stream_t stream);
+                                   int64_t G, int64_t dim, int64_t vdim, float eps, float* raw_workspace /*nullable*/,
+                                   int64_t rows, int dtype, b200_stream_t stream);
 /* p = softmax(router_weight h) over E outputs (fp32); choice score c = p + correction (nullable); the outputs form
  * n_groups equal runs of neighbours and only the keep_groups runs with the largest max c can be chosen; the `top`
  * largest c are chosen; weights = chosen p / (their sum + weight_eps).  extra_weight (nullable, fp32 [W]):

@@ -173,7 +173,7 @@ SIGNATURES = {
                                         _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                         _f32, _int, _vp]),
     "b200_gated_delta_scan": (_int, [_vp, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64,
-                                     _i64, _i64, _i64, _i64, _f32, _int, _vp]),
+                                     _i64, _i64, _i64, _i64, _f32, _vp, _i64, _int, _vp]),
     "b200_moe_route_softmax": (_int, [_vp, _vp, _vp, _vp, _i64, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                                       _f32, _int, _vp]),
     "b200_moe_combine_weighted": (_int, [_vp, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _i64,

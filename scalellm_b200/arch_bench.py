@@ -753,7 +753,7 @@ def fesupel_kernels_alone(s: dict, peaks: dict, cases=((64, 4096, 1), (4, 2048, 
         dg, dn = rnd(rows, RH * rv), torch.ones(rv, device=dev)
         st = torch.zeros((batch, RH, rd, rv), dtype=torch.float32, device=dev)
         f_gd = lambda: kernels.gated_delta_scan(dq, dk, dv, dd, db, dg, dn, st, prm.q_cu_seq_lens, positions,
-                                                prm.state_slots, 1e-5)
+                                                prm.state_slots, 1e-5, q_len)
         n = RH * rd
         proj = rnd(rows, 5 * n)
         wl = rnd(rows, n)

@@ -292,7 +292,10 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
                         const float* __restrict__ v, const float* __restrict__ decay, const float* __restrict__ beta,
                         const T* __restrict__ gate, int64_t ld_gate, const float* __restrict__ nw,
                         float* __restrict__ state, const int* __restrict__ q_cu, const int* __restrict__ positions,
-                        const int* __restrict__ state_slots, int H, int G, int dim, int vdim, float eps) {
+                        const int* __restrict__ state_slots, int H, int G, int dim, int vdim, float eps,
+                        float* __restrict__ raw) {
+  // raw != nullptr: the read-outs leave as they are (fp32 [rows, H * vdim]) and a token-parallel launch applies the
+  // norm and the gate afterwards, so that the walk has one barrier per token instead of two and no reduction
   constexpr int DL = DK / KS;                       // key rows a thread keeps
   __shared__ __align__(16) float q_s[2][DK], k_s[2][DK], w_s[2][DK];
   __shared__ float red[32];
@@ -368,6 +371,11 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
 #pragma unroll
     for (int sh = KS / 2; sh > 0; sh >>= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
     if (!live) o = 0.0f;
+    if (raw) {              // (the barrier of the next token orders this token's reads before the token after next
+                            // overwrites the same staging buffer)
+      if (live && part == 0) raw[(size_t)t * nv + (size_t)h * vdim + j] = o;
+      continue;
+    }
     const float o2 = block_sum<NT>(part == 0 ? o * o : 0.0f, red);   // its barrier also orders this token's reads
                                                                      // before the token after next overwrites the
                                                                      // same staging buffer
@@ -383,6 +391,27 @@ gated_delta_scan_kernel(T* __restrict__ out, int64_t ldo, const float* __restric
   }
 }
 
+// out[row, h] = raw / rms(raw) * nw * sigmoid(gate): a warp per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_kernel(T* __restrict__ out, int64_t ldo, const float* __restrict__ raw, const T* __restrict__ gate,
+                      int64_t ld_gate, const float* __restrict__ nw, int64_t n_units, int H, int vdim, float eps) {
+  const int64_t u = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (u >= n_units) return;
+  const int64_t row = u / H;
+  const int h = (int)(u - row * H);
+  const float* r = raw + (size_t)u * vdim;
+  float ss = 0.0f;
+  for (int i = lane; i < vdim; i += 32) ss += r[i] * r[i];
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)vdim + eps);
+  for (int i = lane; i < vdim; i += 32) {
+    const float gt = 1.0f / (1.0f + expf(-Num<T>::to_f(gate[(size_t)row * ld_gate + (size_t)h * vdim + i])));
+    out[(size_t)row * ldo + (size_t)h * vdim + i] = Num<T>::from_f(r[i] * inv * nw[i] * gt);
+  }
+}
+
 #define GD_DISPATCH(dtype, ...)                                                  \
   switch (dtype) {                                                               \
     case B200_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }             \
@@ -395,11 +424,11 @@ template <typename T, int DK>
 int launch_gd_scan(int nt, dim3 grid, cudaStream_t st, void* out, int64_t ldo, const float* q, const float* k,
                    const float* v, const float* decay, const float* beta, const void* gate, int64_t ld_gate,
                    const float* nw, float* state, const int* q_cu, const int* positions, const int* slots, int H,
-                   int G, int dim, int vdim, float eps) {
+                   int G, int dim, int vdim, float eps, float* raw, int64_t rows) {
 #define GD_NT(N, KSP)                                                                                              \
   gated_delta_scan_kernel<T, DK, N, KSP><<<grid, N, 0, st>>>(static_cast<T*>(out), ldo, q, k, v, decay, beta,        \
                                                              static_cast<const T*>(gate), ld_gate, nw, state, q_cu, \
-                                                             positions, slots, H, G, dim, vdim, eps)
+                                                             positions, slots, H, G, dim, vdim, eps, raw)
   if constexpr (DK > 128) {          // two threads per column: value sizes up to 128
     if (nt <= 32) GD_NT(64, 2);
     else if (nt <= 64) GD_NT(128, 2);
@@ -413,6 +442,12 @@ int launch_gd_scan(int nt, dim3 grid, cudaStream_t st, void* out, int64_t ldo, c
   }
 #undef GD_NT
   B200_LAUNCH_OK("gated_delta_scan_kernel");
+  if (raw) {
+    const int64_t n_units = rows * H;
+    head_norm_gate_kernel<T><<<(unsigned)((n_units + 7) / 8), 256, 0, st>>>(
+        static_cast<T*>(out), ldo, raw, static_cast<const T*>(gate), ld_gate, nw, n_units, H, vdim, eps);
+    B200_LAUNCH_OK("head_norm_gate_kernel");
+  }
   return B200_OK;
 }
 
@@ -465,7 +500,7 @@ int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k
                           const float* beta, const void* gate_logits, int64_t ld_gate, const float* norm_weight,
                           float* state, const int32_t* q_cu_lens, const int32_t* positions,
                           const int32_t* state_slots, int64_t n_seq, int64_t H, int64_t G, int64_t dim, int64_t vdim,
-                          float eps, int dtype, b200_stream_t stream) {
+                          float eps, float* raw_workspace, int64_t rows, int dtype, b200_stream_t stream) {
   if (n_seq == 0) return B200_OK;
   B200_CHECK_ARG(out && q && k && v && decay && beta && gate_logits && norm_weight && state && q_cu_lens &&
                      positions && state_slots,
@@ -479,7 +514,7 @@ int b200_gated_delta_scan(void* out, int64_t ldo, const float* q, const float* k
 #define GD_CALL(DK)                                                                                                  \
   GD_DISPATCH(dtype, return (launch_gd_scan<T, DK>(nt, grid, st, out, ldo, q, k, v, decay, beta, gate_logits, ld_gate, \
                                                    norm_weight, state, q_cu_lens, positions, state_slots, (int)H,     \
-                                                   (int)G, (int)dim, (int)vdim, eps)))
+                                                   (int)G, (int)dim, (int)vdim, eps, raw_workspace, rows)))
   if (dim <= 32) { GD_CALL(32); }
   else if (dim <= 64) { GD_CALL(64); }
   else if (dim <= 128) { GD_CALL(128); }

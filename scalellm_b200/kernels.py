@@ -1407,12 +1407,18 @@ def gated_delta_prepare(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tens
     return q, k, v, decay, beta
 
 
+# a step whose longest portion has at least this many tokens norms and gates the read-outs in a launch of its own
+GATED_DELTA_SPLIT_NORM_MIN_ROWS = 16
+
+
 def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor,
                      gate_logits: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor, q_cu: torch.Tensor,
-                     positions: torch.Tensor, state_slots: torch.Tensor, eps: float) -> torch.Tensor:
+                     positions: torch.Tensor, state_slots: torch.Tensor, eps: float, q_max: int = 1) -> torch.Tensor:
     """The recurrence S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q per (sequence, head) over
     the step's rows in order, state fp32 [n_slots, H, dim, vdim] updated in place; returns
-    o / rms(o) * norm_weight * sigmoid(gate_logits) as [rows, H * vdim] in gate_logits' dtype."""
+    o / rms(o) * norm_weight * sigmoid(gate_logits) as [rows, H * vdim] in gate_logits' dtype.  q_max: the step's
+    longest portion (a host number): long portions leave the walk with plain read-outs and take norm and gate in a
+    token-parallel launch, which spares the walk a barrier and a reduction per token."""
     _cuda(q, k, v, decay, beta, gate_logits, norm_weight, state)
     _f32(q, k, v, decay, beta, norm_weight, state)
     _check_i32(q_cu, positions, state_slots)
@@ -1422,10 +1428,13 @@ def gated_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: t
     assert gate_logits.shape == (rows, H * vdim) and gate_logits.stride(1) == 1
     assert norm_weight.numel() == vdim and state.shape[1:] == (H, dim, vdim)
     out = torch.empty((rows, H * vdim), dtype=gate_logits.dtype, device=q.device)
+    raw = None
+    if q_max >= GATED_DELTA_SPLIT_NORM_MIN_ROWS:
+        raw = torch.empty((rows, H * vdim), dtype=torch.float32, device=q.device)
     check(_lib.load().b200_gated_delta_scan(_p(out), H * vdim, _p(q), _p(k), _p(v), _p(decay), _p(beta),
                                             _p(gate_logits), gate_logits.stride(0), _p(norm_weight), _p(state),
                                             _p(q_cu), _p(positions), _p(state_slots), state_slots.numel(), H, G, dim,
-                                            vdim, eps, _dt(gate_logits), _stream()))
+                                            vdim, eps, _p(raw), rows, _dt(gate_logits), _stream()))
     return out
 
 

@@ -1147,7 +1147,8 @@ class GatedDeltaMixer:
             params.q_cu_seq_lens, positions, params.token_seq, params.state_slots, self.H, self.G, self.dim, self.vd,
             self.unit_eps)
         o = kernels.gated_delta_scan(q, k, v, decay, beta, low[:, nd:], self.norm_weight, self.state,
-                                     params.q_cu_seq_lens, positions, params.state_slots, self.eps)
+                                     params.q_cu_seq_lens, positions, params.state_slots, self.eps,
+                                     params.q_max_seq_len)
         return self.o_proj(o)
 
     def forward(self, h: torch.Tensor, positions: torch.Tensor, params: InputParameters) -> torch.Tensor:

@@ -383,7 +383,7 @@ def test_gated_delta_rule_filters_and_state_over_portions(dtype, H, G, dim, vdim
             dec, w["q.conv"], w["k.conv"], w["v.conv"], w["A_log"], w["dt_bias"], fstate, par.q_cu_seq_lens, pos,
             par.token_seq, par.state_slots, H, G, dim, vdim, 1e-6)
         o = kernels.gated_delta_scan(q, k, v, decay, beta, gate, w["norm"], state, par.q_cu_seq_lens, pos,
-                                     par.state_slots, eps)
+                                     par.state_slots, eps, 16 if step % 2 else 1)      # both ends of the walk
         got[0].append(o[:ns[0]].cpu())
         got[1].append(o[ns[0]:].cpu())
         at[0] += ns[0]
@@ -417,7 +417,7 @@ def test_gated_delta_rule_decodes_long(dtype):
                 wd["q.conv"], wd["k.conv"], wd["v.conv"], wd["A_log"], wd["dt_bias"], fstate, par.q_cu_seq_lens, pos,
                 par.token_seq, par.state_slots, H, G, dim, vdim, 1e-6)
             out.append(kernels.gated_delta_scan(q, k, v, decay, beta, g_, wd["norm"], state, par.q_cu_seq_lens, pos,
-                                                par.state_slots, 1e-5).cpu())
+                                                par.state_slots, 1e-5, c).cpu())
             at += c
         outs[name] = torch.cat(out).double()
         tol = 3e-4 if dtype == torch.float32 else 5e-2
